@@ -1,0 +1,442 @@
+// Host side of the C ABI (include/moe_b200.h): context, weight ingestion and
+// the launch sequence of one MoE block.  It mirrors, call for call, what the
+// reference runtime does around its MoE kernels (getp-csrc/getp_run.cpp:
+// malloc_gpu_run_state*, copy_weights_to_gpu_*, moe_gpu / moe_gpu_120b), minus
+// the host synchronisations: nothing in moe_forward() waits for the device.
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
+#include "moe_internal.cuh"
+
+using namespace moe;
+
+namespace {
+
+int fail(moe_ctx *c, int code, const char *fmt, ...) {
+  if (c) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    c->err = buf;
+  }
+  return code;
+}
+
+#define CU_TRY(c, expr)                                                                       \
+  do {                                                                                        \
+    cudaError_t e__ = (expr);                                                                 \
+    if (e__ != cudaSuccess)                                                                   \
+      return fail((c), e__ == cudaErrorMemoryAllocation ? MOE_ERR_NOMEM : MOE_ERR_CUDA,       \
+                  "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__), __FILE__, __LINE__); \
+  } while (0)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// Packed weight codes viewed as bytes: [E][R][K/2], box = 64 bytes x 256 rows x 1.
+int make_weight_map(moe_ctx *c, CUtensorMap *m, const uint8_t *base, int E, int R, int K) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(c, MOE_ERR_CUDA, "cuTensorMapEncodeTiled not available");
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(K / 2), static_cast<cuuint64_t>(R), static_cast<cuuint64_t>(E)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(K / 2), static_cast<cuuint64_t>(R) * (K / 2)};
+  const cuuint32_t box[3] = {kChunkK / 2, kPairRows, 1};
+  const cuuint32_t es[3] = {1, 1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t *>(base), dims, strides, box, es,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(c, MOE_ERR_CUDA, "cuTensorMapEncodeTiled(weights E=%d R=%d K=%d) -> %d", E, R, K, (int)r);
+  return MOE_OK;
+}
+
+// fp16 activations [rows][K], box = 64 elements x 32 rows, 128-byte swizzle.
+int make_act_map(moe_ctx *c, CUtensorMap *m, const __half *base, int rows, int K) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(c, MOE_ERR_CUDA, "cuTensorMapEncodeTiled not available");
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * 2};
+  const cuuint32_t box[2] = {kSubK, kXBoxRows};
+  const cuuint32_t es[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half *>(base), dims, strides, box, es,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(c, MOE_ERR_CUDA, "cuTensorMapEncodeTiled(activations rows=%d K=%d) -> %d", rows, K, (int)r);
+  return MOE_OK;
+}
+
+uint16_t f32_to_bf16_rn(float f) {
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  u += 0x7FFFu + ((u >> 16) & 1u);
+  return static_cast<uint16_t>(u >> 16);
+}
+float bf16_to_f32(uint16_t b) {
+  uint32_t u = static_cast<uint32_t>(b) << 16;
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+
+template <class T>
+int dev_alloc(moe_ctx *c, T **p, size_t n) {
+  CU_TRY(c, cudaMalloc(reinterpret_cast<void **>(p), n * sizeof(T) + 256));
+  return MOE_OK;
+}
+
+// E8M0 scales of one weight matrix -> [E][n_pairs][n_kchunks][256 rows][4], 127 where no block exists.
+void tile_scales(const uint8_t *raw /*[E][R][nblk]*/, int E, int R, int nblk, int n_pairs, int n_kc,
+                 std::vector<uint8_t> &out) {
+  out.assign(static_cast<size_t>(E) * n_pairs * n_kc * kScaleChunkBytes, 127);
+  for (int e = 0; e < E; ++e)
+    for (int r = 0; r < R; ++r) {
+      const uint8_t *src = raw + (static_cast<size_t>(e) * R + r) * nblk;
+      const int pair = r / kPairRows, rb = r % kPairRows;
+      for (int b = 0; b < nblk; ++b) {
+        const int kc = b / 4, c = b % 4;
+        out[((static_cast<size_t>(e) * n_pairs + pair) * n_kc + kc) * kScaleChunkBytes + rb * 4 + c] = src[b];
+      }
+    }
+}
+
+void free_layer(LayerWeights &w) {
+  cudaFree(w.w1_codes); cudaFree(w.w1_scales); cudaFree(w.b1);
+  cudaFree(w.w2_codes); cudaFree(w.w2_scales); cudaFree(w.b2);
+  cudaFree(w.w1_scales_raw); cudaFree(w.w2_scales_raw);
+  cudaFree(w.router_w3); cudaFree(w.router_b);
+  w = LayerWeights();
+}
+
+}  // namespace
+
+extern "C" {
+
+const char *moe_strerror(int code) {
+  switch (code) {
+    case MOE_OK: return "ok";
+    case MOE_ERR_INVALID: return "invalid argument";
+    case MOE_ERR_CUDA: return "CUDA error";
+    case MOE_ERR_NOMEM: return "out of memory";
+    case MOE_ERR_TIMEOUT: return "a bounded wait ran out";
+    case MOE_ERR_SCALE_RANGE: return "E8M0 scale outside the fp16-exact range";
+    case MOE_ERR_STATE: return "wrong state";
+    case MOE_ERR_NO_SM100: return "device is not sm_100";
+    default: return "unknown";
+  }
+}
+
+const char *moe_last_error(moe_handle h) { return h ? h->err.c_str() : "null handle"; }
+long long moe_launch_count(moe_handle h) { return h ? h->launches : 0; }
+
+int moe_shard_range(int D, int tp_size, int tp_rank, int *start, int *len) {
+  if (D <= 0 || D % 32 || tp_size <= 0 || tp_rank < 0 || tp_rank >= tp_size || D / 32 < tp_size) return MOE_ERR_INVALID;
+  const int nblk = D / 32, base = nblk / tp_size, rem = nblk % tp_size;
+  const int l = base + (tp_rank < rem ? 1 : 0);
+  const int s = tp_rank * base + (tp_rank < rem ? tp_rank : rem);
+  if (start) *start = s * 32;
+  if (len) *len = l * 32;
+  return MOE_OK;
+}
+
+int moe_create(const moe_config *cfg, moe_handle *out) {
+  if (!cfg || !out) return MOE_ERR_INVALID;
+  *out = nullptr;
+  if (cfg->hidden_dim <= 0 || cfg->hidden_dim % 32 || cfg->intermediate_dim <= 0 || cfg->intermediate_dim % 32 ||
+      cfg->n_experts <= 0 || cfg->n_experts > 256 || cfg->experts_per_token <= 0 || cfg->experts_per_token > 8 ||
+      cfg->experts_per_token > cfg->n_experts || cfg->n_layers <= 0 || cfg->max_rows <= 0 || cfg->tp_size <= 0 ||
+      cfg->tp_rank < 0 || cfg->tp_rank >= cfg->tp_size)
+    return MOE_ERR_INVALID;
+  moe_ctx *c = new (std::nothrow) moe_ctx();
+  if (!c) return MOE_ERR_NOMEM;
+  *out = c;  // returned even on failure so the caller can read moe_last_error(); moe_destroy() frees it
+  c->cfg = *cfg;
+  c->H = cfg->hidden_dim; c->D = cfg->intermediate_dim; c->E = cfg->n_experts;
+  c->K = cfg->experts_per_token; c->L = cfg->n_layers;
+  if (moe_shard_range(c->D, cfg->tp_size, cfg->tp_rank, &c->d0, &c->Dl) != MOE_OK)
+    return fail(c, MOE_ERR_INVALID, "intermediate_dim %d cannot be split over %d ranks on 32-element boundaries", c->D, cfg->tp_size);
+  c->R1 = 2 * c->Dl;
+  c->max_rows = cfg->max_rows;
+  c->max_pairs = cfg->max_rows * c->K;
+  c->layers.resize(c->L);
+
+  CU_TRY(c, cudaSetDevice(cfg->device));
+  cudaDeviceProp prop;
+  CU_TRY(c, cudaGetDeviceProperties(&prop, cfg->device));
+  if (prop.major != 10) return fail(c, MOE_ERR_NO_SM100, "device %d is sm_%d%d; this library is sm_100a only", cfg->device, prop.major, prop.minor);
+  c->sm_count = prop.multiProcessorCount;
+  CU_TRY(c, cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+  CU_TRY(c, expert_gemm_init());
+
+  const size_t T = c->max_rows, P = c->max_pairs;
+  int rc;
+  if ((rc = dev_alloc(c, &c->t_in, T * c->H))) return rc;
+  if ((rc = dev_alloc(c, &c->logits, T * c->E))) return rc;
+  if ((rc = dev_alloc(c, &c->topk_idx, T * c->K))) return rc;
+  if ((rc = dev_alloc(c, &c->topk_w, T * c->K))) return rc;
+  if ((rc = dev_alloc(c, &c->counts, (size_t)c->E))) return rc;
+  if ((rc = dev_alloc(c, &c->offsets, (size_t)c->E + 1))) return rc;
+  if ((rc = dev_alloc(c, &c->pair_row, T * c->K))) return rc;
+  if ((rc = dev_alloc(c, &c->row_token, P))) return rc;
+  if ((rc = dev_alloc(c, &c->xperm, P * c->H))) return rc;
+  if ((rc = dev_alloc(c, &c->hbuf, P * c->Dl))) return rc;
+  if ((rc = dev_alloc(c, &c->ybuf, P * c->H))) return rc;
+  if ((rc = dev_alloc(c, &c->out_f32, T * c->H))) return rc;
+  if ((rc = dev_alloc(c, &c->out_bf16, T * c->H))) return rc;
+  const int n_pairs1 = (c->R1 + kPairRows - 1) / kPairRows, n_pairs2 = (c->H + kPairRows - 1) / kPairRows;
+  const int max_tiles = c->max_pairs / kTokTile + c->E + 1;
+  c->max_work1 = max_tiles * n_pairs1;
+  c->max_work2 = max_tiles * n_pairs2;
+  if ((rc = dev_alloc(c, &c->work1, (size_t)c->max_work1))) return rc;
+  if ((rc = dev_alloc(c, &c->work2, (size_t)c->max_work2))) return rc;
+  if ((rc = dev_alloc(c, &c->n_work, (size_t)2))) return rc;
+  if ((rc = dev_alloc(c, &c->status, (size_t)1))) return rc;
+  CU_TRY(c, cudaMemset(c->status, 0, sizeof(unsigned)));
+  CU_TRY(c, cudaMemset(c->n_work, 0, 2 * sizeof(int)));
+  // Rows past the current batch are read (and discarded) by token tiles that overhang; keep them finite.
+  CU_TRY(c, cudaMemset(c->xperm, 0, P * c->H * sizeof(__half)));
+  CU_TRY(c, cudaMemset(c->hbuf, 0, P * c->Dl * sizeof(__half)));
+  if ((rc = make_act_map(c, &c->tm_x1, c->xperm, c->max_pairs, c->H))) return rc;
+  if ((rc = make_act_map(c, &c->tm_x2, c->hbuf, c->max_pairs, c->Dl))) return rc;
+  return MOE_OK;
+}
+
+int moe_destroy(moe_handle c) {
+  if (!c) return MOE_ERR_INVALID;
+  cudaSetDevice(c->cfg.device);
+  if (c->stream) { cudaStreamSynchronize(c->stream); cudaStreamDestroy(c->stream); }
+  for (auto &w : c->layers) free_layer(w);
+  cudaFree(c->t_in); cudaFree(c->logits); cudaFree(c->topk_idx); cudaFree(c->topk_w); cudaFree(c->counts);
+  cudaFree(c->offsets); cudaFree(c->pair_row); cudaFree(c->row_token); cudaFree(c->xperm); cudaFree(c->hbuf);
+  cudaFree(c->ybuf); cudaFree(c->out_f32); cudaFree(c->out_bf16); cudaFree(c->work1); cudaFree(c->work2);
+  cudaFree(c->n_work); cudaFree(c->status);
+  delete c;
+  return MOE_OK;
+}
+
+int moe_load_layer(moe_handle c, int layer, const uint8_t *w1_codes, const uint8_t *w1_scales, const uint16_t *b1,
+                   const uint8_t *w2_codes, const uint8_t *w2_scales, const uint16_t *b2, const float *router_w,
+                   const float *router_b) {
+  if (!c) return MOE_ERR_INVALID;
+  if (layer < 0 || layer >= c->L || !w1_codes || !w1_scales || !b1 || !w2_codes || !w2_scales || !b2 || !router_w || !router_b)
+    return fail(c, MOE_ERR_INVALID, "moe_load_layer: bad layer index or null tensor");
+  CU_TRY(c, cudaSetDevice(c->cfg.device));
+  const int E = c->E, H = c->H, D = c->D, Dl = c->Dl, d0 = c->d0, R1 = c->R1;
+  LayerWeights &w = c->layers[layer];
+  free_layer(w);
+
+  // ---- this rank's shard, still in the reference layout -------------------
+  // MLP1: rows [2*d0, 2*(d0+Dl)) of every expert (gate/up pairs stay adjacent);
+  // MLP2: columns [d0, d0+Dl).  Scale blocks (32 along the input dim) are never cut.
+  const size_t w1_row = H / 2, s1_row = H / 32;
+  std::vector<uint8_t> c1(static_cast<size_t>(E) * R1 * w1_row), s1(static_cast<size_t>(E) * R1 * s1_row);
+  std::vector<uint16_t> bb1(static_cast<size_t>(E) * R1);
+  for (int e = 0; e < E; ++e) {
+    const size_t src_row0 = static_cast<size_t>(e) * 2 * D + 2 * d0;
+    memcpy(&c1[static_cast<size_t>(e) * R1 * w1_row], w1_codes + src_row0 * w1_row, static_cast<size_t>(R1) * w1_row);
+    memcpy(&s1[static_cast<size_t>(e) * R1 * s1_row], w1_scales + src_row0 * s1_row, static_cast<size_t>(R1) * s1_row);
+    memcpy(&bb1[static_cast<size_t>(e) * R1], b1 + src_row0, static_cast<size_t>(R1) * 2);
+  }
+  const size_t w2_row = Dl / 2, s2_row = Dl / 32;
+  std::vector<uint8_t> c2(static_cast<size_t>(E) * H * w2_row), s2(static_cast<size_t>(E) * H * s2_row);
+  for (size_t r = 0; r < static_cast<size_t>(E) * H; ++r) {
+    memcpy(&c2[r * w2_row], w2_codes + r * (D / 2) + d0 / 2, w2_row);
+    memcpy(&s2[r * s2_row], w2_scales + r * (D / 32) + d0 / 32, s2_row);
+  }
+  // every scaled code must be an exact fp16 value: exponent in [-23, 13]
+  for (const std::vector<uint8_t> *sv : {&s1, &s2})
+    for (uint8_t b : *sv) {
+      const int e8 = static_cast<int>(b) - 127;
+      if (e8 < -23 || e8 > 13)
+        return fail(c, MOE_ERR_SCALE_RANGE, "layer %d: E8M0 exponent %d outside [-23, 13]", layer, e8);
+    }
+
+  const int n_pairs1 = (R1 + kPairRows - 1) / kPairRows, n_kc1 = (H + kChunkK - 1) / kChunkK;
+  const int n_pairs2 = (H + kPairRows - 1) / kPairRows, n_kc2 = (Dl + kChunkK - 1) / kChunkK;
+  std::vector<uint8_t> t1, t2;
+  tile_scales(s1.data(), E, R1, H / 32, n_pairs1, n_kc1, t1);
+  tile_scales(s2.data(), E, H, Dl / 32, n_pairs2, n_kc2, t2);
+
+  // router weight as three bf16 planes whose sum is the fp32 value exactly
+  std::vector<uint16_t> w3(static_cast<size_t>(3) * E * H);
+  for (size_t i = 0; i < static_cast<size_t>(E) * H; ++i) {
+    const float v = router_w[i];
+    const uint16_t hi = f32_to_bf16_rn(v);
+    const float r1 = v - bf16_to_f32(hi);
+    const uint16_t mid = f32_to_bf16_rn(r1);
+    const float r2 = r1 - bf16_to_f32(mid);
+    const uint16_t lo = f32_to_bf16_rn(r2);
+    w3[i] = hi;
+    w3[static_cast<size_t>(E) * H + i] = mid;
+    w3[static_cast<size_t>(2) * E * H + i] = lo;
+  }
+
+  int rc;
+  if ((rc = dev_alloc(c, &w.w1_codes, c1.size()))) return rc;
+  if ((rc = dev_alloc(c, &w.w1_scales, t1.size()))) return rc;
+  if ((rc = dev_alloc(c, &w.w1_scales_raw, s1.size()))) return rc;
+  if ((rc = dev_alloc(c, &w.b1, bb1.size()))) return rc;
+  if ((rc = dev_alloc(c, &w.w2_codes, c2.size()))) return rc;
+  if ((rc = dev_alloc(c, &w.w2_scales, t2.size()))) return rc;
+  if ((rc = dev_alloc(c, &w.w2_scales_raw, s2.size()))) return rc;
+  if ((rc = dev_alloc(c, &w.b2, static_cast<size_t>(E) * H))) return rc;
+  if ((rc = dev_alloc(c, &w.router_w3, w3.size()))) return rc;
+  if ((rc = dev_alloc(c, &w.router_b, static_cast<size_t>(E)))) return rc;
+  CU_TRY(c, cudaMemcpy(w.w1_codes, c1.data(), c1.size(), cudaMemcpyHostToDevice));
+  CU_TRY(c, cudaMemcpy(w.w1_scales, t1.data(), t1.size(), cudaMemcpyHostToDevice));
+  CU_TRY(c, cudaMemcpy(w.w1_scales_raw, s1.data(), s1.size(), cudaMemcpyHostToDevice));
+  CU_TRY(c, cudaMemcpy(w.b1, bb1.data(), bb1.size() * 2, cudaMemcpyHostToDevice));
+  CU_TRY(c, cudaMemcpy(w.w2_codes, c2.data(), c2.size(), cudaMemcpyHostToDevice));
+  CU_TRY(c, cudaMemcpy(w.w2_scales, t2.data(), t2.size(), cudaMemcpyHostToDevice));
+  CU_TRY(c, cudaMemcpy(w.w2_scales_raw, s2.data(), s2.size(), cudaMemcpyHostToDevice));
+  CU_TRY(c, cudaMemcpy(w.b2, b2, static_cast<size_t>(E) * H * 2, cudaMemcpyHostToDevice));
+  CU_TRY(c, cudaMemcpy(w.router_w3, w3.data(), w3.size() * 2, cudaMemcpyHostToDevice));
+  CU_TRY(c, cudaMemcpy(w.router_b, router_b, static_cast<size_t>(E) * 4, cudaMemcpyHostToDevice));
+  if ((rc = make_weight_map(c, &w.tm_w1, w.w1_codes, E, R1, H))) return rc;
+  if ((rc = make_weight_map(c, &w.tm_w2, w.w2_codes, E, H, Dl))) return rc;
+  w.loaded = true;
+  return MOE_OK;
+}
+
+int moe_route_topk(moe_handle c, const float *logits_dev, int rows, int *idx_dev, float *w_dev, void *stream) {
+  if (!c || !logits_dev || !idx_dev || !w_dev || rows <= 0) return MOE_ERR_INVALID;
+  CU_TRY(c, cudaSetDevice(c->cfg.device));
+  launch_topk_softmax(logits_dev, rows, c->E, c->K, idx_dev, w_dev, nullptr, static_cast<cudaStream_t>(stream));
+  c->launches += 1;
+  CU_TRY(c, cudaGetLastError());
+  return MOE_OK;
+}
+
+int moe_forward(moe_handle c, int layer, const void *t_dev, int rows, void *out_dev, unsigned flags, void *stream) {
+  if (!c) return MOE_ERR_INVALID;
+  if (layer < 0 || layer >= c->L || !t_dev || rows <= 0 || rows > c->max_rows)
+    return fail(c, MOE_ERR_INVALID, "moe_forward: layer %d rows %d (max %d)", layer, rows, c->max_rows);
+  if (!out_dev && !(flags & MOE_FWD_PARTIAL_F32)) return fail(c, MOE_ERR_INVALID, "moe_forward: null output");
+  LayerWeights &w = c->layers[layer];
+  if (!w.loaded) return fail(c, MOE_ERR_STATE, "layer %d has no weights", layer);
+  CU_TRY(c, cudaSetDevice(c->cfg.device));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int T = rows, P = rows * c->K, E = c->E, H = c->H, K = c->K;
+  const __nv_bfloat16 *t = static_cast<const __nv_bfloat16 *>(t_dev);
+  const int n_pairs1 = (c->R1 + kPairRows - 1) / kPairRows, n_pairs2 = (H + kPairRows - 1) / kPairRows;
+
+  CU_TRY(c, cudaMemsetAsync(c->counts, 0, sizeof(int) * E, s));
+  launch_router_logits(t, w.router_w3, w.router_b, c->logits, T, H, E, s);
+  launch_topk_softmax(c->logits, T, E, K, c->topk_idx, c->topk_w, c->counts, s);
+  launch_build_index(c->topk_idx, c->counts, T, E, K, n_pairs1, n_pairs2, c->offsets, c->pair_row, c->row_token,
+                     c->work1, c->work2, c->n_work, c->max_work1, c->max_work2, c->status, s);
+  launch_gather_rows(t, c->row_token, c->offsets, E, c->xperm, H, P, s);
+  const int add_b2 = c->cfg.tp_rank == 0 ? 1 : 0;
+  if (flags & MOE_FWD_SIMT_GEMM) {
+    launch_simt_mlp1(w.w1_codes, w.w1_scales_raw, w.b1, c->xperm, c->offsets, E, H, c->R1, c->hbuf,
+                     c->cfg.swiglu_limit, c->cfg.swiglu_alpha, P, s);
+    launch_simt_mlp2(w.w2_codes, w.w2_scales_raw, w.b2, add_b2, c->hbuf, c->offsets, E, c->Dl, H, c->ybuf, P, s);
+  } else {
+    GemmArgs a{};
+    a.work = c->work1; a.n_work = c->n_work; a.K = H; a.R = c->R1;
+    a.n_kchunks = (H + kChunkK - 1) / kChunkK; a.n_pairs = n_pairs1;
+    a.scales = w.w1_scales; a.bias = w.b1; a.add_bias = 1;
+    a.h_out = c->hbuf; a.y_out = nullptr; a.ld_out = c->Dl;
+    a.limit = c->cfg.swiglu_limit; a.alpha = c->cfg.swiglu_alpha; a.status = c->status;
+    launch_expert_gemm_mlp1(w.tm_w1, c->tm_x1, a, c->sm_count, s);
+    GemmArgs b = a;
+    b.work = c->work2; b.n_work = c->n_work + 1; b.K = c->Dl; b.R = H;
+    b.n_kchunks = (c->Dl + kChunkK - 1) / kChunkK; b.n_pairs = n_pairs2;
+    b.scales = w.w2_scales; b.bias = w.b2; b.add_bias = add_b2;
+    b.h_out = nullptr; b.y_out = c->ybuf; b.ld_out = H;
+    launch_expert_gemm_mlp2(w.tm_w2, c->tm_x2, b, c->sm_count, s);
+  }
+  const bool partial = (flags & MOE_FWD_PARTIAL_F32) != 0;
+  const bool keep_f32 = partial || (c->cfg.flags & MOE_CFG_KEEP_F32_OUT);
+  launch_combine(c->ybuf, c->topk_idx, c->topk_w, c->pair_row, T, H, K,
+                 partial ? nullptr : static_cast<__nv_bfloat16 *>(out_dev), keep_f32 ? c->out_f32 : nullptr, s);
+  c->launches += 7;
+  c->last_rows = rows;
+  CU_TRY(c, cudaGetLastError());
+  return MOE_OK;
+}
+
+int moe_synchronize(moe_handle c) {
+  if (!c) return MOE_ERR_INVALID;
+  CU_TRY(c, cudaSetDevice(c->cfg.device));
+  CU_TRY(c, cudaDeviceSynchronize());
+  unsigned st = 0;
+  CU_TRY(c, cudaMemcpy(&st, c->status, sizeof(st), cudaMemcpyDeviceToHost));
+  if (st) {
+    CU_TRY(c, cudaMemset(c->status, 0, sizeof(unsigned)));
+    return fail(c, (st & ST_BAD_INDEX) ? MOE_ERR_STATE : MOE_ERR_TIMEOUT, "device status word 0x%x", st);
+  }
+  return MOE_OK;
+}
+
+int moe_forward_host(moe_handle c, int layer, const void *t_host, int rows, void *out_host, unsigned flags) {
+  if (!c) return MOE_ERR_INVALID;
+  if (!t_host || !out_host || rows <= 0 || rows > c->max_rows) return fail(c, MOE_ERR_INVALID, "moe_forward_host: bad arguments");
+  CU_TRY(c, cudaSetDevice(c->cfg.device));
+  const size_t bytes = static_cast<size_t>(rows) * c->H * 2;
+  CU_TRY(c, cudaMemcpyAsync(c->t_in, t_host, bytes, cudaMemcpyHostToDevice, c->stream));
+  int rc = moe_forward(c, layer, c->t_in, rows, c->out_bf16, flags & ~MOE_FWD_PARTIAL_F32, c->stream);
+  if (rc != MOE_OK) return rc;
+  CU_TRY(c, cudaMemcpyAsync(out_host, c->out_bf16, bytes, cudaMemcpyDeviceToHost, c->stream));
+  CU_TRY(c, cudaStreamSynchronize(c->stream));
+  unsigned st = 0;
+  CU_TRY(c, cudaMemcpy(&st, c->status, sizeof(st), cudaMemcpyDeviceToHost));
+  if (st) {
+    CU_TRY(c, cudaMemset(c->status, 0, sizeof(unsigned)));
+    return fail(c, (st & ST_BAD_INDEX) ? MOE_ERR_STATE : MOE_ERR_TIMEOUT, "device status word 0x%x", st);
+  }
+  return MOE_OK;
+}
+
+void *moe_host_alloc(size_t bytes) {
+  void *p = nullptr;
+  if (cudaHostAlloc(&p, bytes, cudaHostAllocDefault) != cudaSuccess) return nullptr;
+  return p;
+}
+void moe_host_free(void *p) {
+  if (p) cudaFreeHost(p);
+}
+
+int moe_get_debug(moe_handle c, int which, void *dst, size_t bytes) {
+  if (!c || !dst) return MOE_ERR_INVALID;
+  CU_TRY(c, cudaSetDevice(c->cfg.device));
+  const size_t T = c->last_rows;
+  const void *src = nullptr;
+  size_t have = 0;
+  switch (which) {
+    case MOE_DBG_LOGITS: src = c->logits; have = T * c->E * 4; break;
+    case MOE_DBG_TOPK_IDX: src = c->topk_idx; have = T * c->K * 4; break;
+    case MOE_DBG_TOPK_W: src = c->topk_w; have = T * c->K * 4; break;
+    case MOE_DBG_COUNTS: src = c->counts; have = (size_t)c->E * 4; break;
+    case MOE_DBG_OFFSETS: src = c->offsets; have = ((size_t)c->E + 1) * 4; break;
+    case MOE_DBG_PAIR_ROW: src = c->pair_row; have = T * c->K * 4; break;
+    case MOE_DBG_ROW_TOKEN: src = c->row_token; have = T * c->K * 4; break;
+    case MOE_DBG_OUT_F32: src = c->out_f32; have = T * c->H * 4; break;
+    case MOE_DBG_STATUS: src = c->status; have = 4; break;
+    case MOE_DBG_HBUF: src = c->hbuf; have = T * c->K * c->Dl * 2; break;
+    case MOE_DBG_YBUF: src = c->ybuf; have = T * c->K * c->H * 4; break;
+    default: return fail(c, MOE_ERR_INVALID, "moe_get_debug: unknown item %d", which);
+  }
+  if (bytes > have) return fail(c, MOE_ERR_INVALID, "moe_get_debug: %zu bytes asked, %zu available", bytes, have);
+  CU_TRY(c, cudaDeviceSynchronize());
+  CU_TRY(c, cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToHost));
+  return MOE_OK;
+}
+
+}  // extern "C"

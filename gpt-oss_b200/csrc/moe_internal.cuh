@@ -1,0 +1,144 @@
+// Internal structures shared by the host API and the kernels of the MoE block.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/moe_b200.h"
+
+namespace moe {
+
+// ---- tiling constants of the expert GEMM (expert_gemm_sm100.cu) -------------
+constexpr int kTileRows = 128;    // weight rows per MMA tile (UMMA M)
+constexpr int kPairRows = 256;    // weight rows per work item (two MMA tiles share one token tile)
+constexpr int kChunkK = 128;      // reduction elements per shared-memory stage
+constexpr int kSubK = 64;         // reduction elements per tensor-memory A buffer
+constexpr int kTokTile = 96;      // most token rows per work item (UMMA N <= 96)
+constexpr int kXBoxRows = 32;     // token rows per TMA box
+constexpr int kScaleChunkBytes = kPairRows * (kChunkK / 32);  // 1024: scales of one stage
+
+// Device status bits (MOE_DBG_STATUS).
+enum : unsigned {
+  ST_WAIT_FULL = 1u,      // expert GEMM: TMA data never arrived
+  ST_WAIT_EMPTY = 2u,     // expert GEMM: stage never released
+  ST_WAIT_AREADY = 4u,    // expert GEMM: dequantised tile never published
+  ST_WAIT_AFREE = 8u,     // expert GEMM: tensor-memory A buffer never released
+  ST_WAIT_DFULL = 16u,    // expert GEMM: accumulator never completed
+  ST_WAIT_DEMPTY = 32u,   // expert GEMM: accumulator never drained
+  ST_BAD_INDEX = 64u,     // routing produced an out-of-range row
+  ST_WAIT_PEER = 128u,    // TP collective: a peer's flag never arrived
+};
+
+// One work item of the grouped GEMM.
+struct __align__(16) WorkItem {
+  int expert;  // expert index
+  int pair;    // 256-row block of that expert's weight matrix
+  int row0;    // first permuted row of the token tile
+  int ntok;    // valid token rows in the tile (1..kTokTile)
+};
+
+struct GemmArgs {
+  const WorkItem *work;
+  const int *n_work;
+  int K;          // reduction length in elements (multiple of 32)
+  int R;          // weight rows per expert on this rank
+  int n_kchunks;  // ceil(K / kChunkK)
+  int n_pairs;    // ceil(R / kPairRows)
+  const uint8_t *scales;      // [E][n_pairs][n_kchunks][256][4] E8M0, padded with 127
+  const __nv_bfloat16 *bias;  // [E][R]
+  int add_bias;               // MLP2 on TP ranks other than 0 leaves the bias out
+  __half *h_out;              // MLP1: [P, ld_out] fp16 SwiGLU output
+  float *y_out;               // MLP2: [P, ld_out] fp32
+  int ld_out;
+  float limit, alpha;
+  unsigned int *status;
+};
+
+struct LayerWeights {
+  bool loaded = false;
+  uint8_t *w1_codes = nullptr;   // [E, R1, H/2]
+  uint8_t *w1_scales = nullptr;  // repacked, see GemmArgs::scales
+  __nv_bfloat16 *b1 = nullptr;   // [E, R1]
+  uint8_t *w2_codes = nullptr;   // [E, H, Dl/2]
+  uint8_t *w2_scales = nullptr;
+  __nv_bfloat16 *b2 = nullptr;   // [E, H]
+  // raw (row-major, unpadded) scales for the validation GEMM
+  uint8_t *w1_scales_raw = nullptr;  // [E, R1, H/32]
+  uint8_t *w2_scales_raw = nullptr;  // [E, H, Dl/32]
+  __nv_bfloat16 *router_w3 = nullptr;  // [3][E][H] exact 3-way bf16 split of the fp32 router weight
+  float *router_b = nullptr;           // [E]
+  CUtensorMap tm_w1, tm_w2;
+};
+
+}  // namespace moe
+
+struct moe_ctx {
+  moe_config cfg;
+  int H, D, E, K, L;
+  int d0, Dl;     // this rank's slice of the intermediate dimension
+  int R1;         // 2*Dl
+  int max_rows, max_pairs;
+  int sm_count;
+  cudaStream_t stream = nullptr;  // used by moe_forward_host
+  std::vector<moe::LayerWeights> layers;
+
+  // run state (names of the reference's GPURunState fields in comments)
+  __nv_bfloat16 *t_in = nullptr;    // gather_x_g          [max_rows, H]
+  float *logits = nullptr;          // router_score_g      [max_rows, E]
+  int *topk_idx = nullptr;          // topk_i_g            [max_rows, K]
+  float *topk_w = nullptr;          // topk_v_g            [max_rows, K]
+  int *counts = nullptr;            // d_expert_counts     [E]
+  int *offsets = nullptr;           // d_expert_offsets    [E+1]
+  int *pair_row = nullptr;          // local_ids_g         [max_rows, K]
+  int *row_token = nullptr;         // expert_row_token_g  [max_pairs]
+  __half *xperm = nullptr;          // expert_input_buffer [max_pairs, H]   fp16
+  __half *hbuf = nullptr;           // gate_up             [max_pairs, Dl]  fp16
+  float *ybuf = nullptr;            // expert_output_partial [max_pairs, H] fp32
+  float *out_f32 = nullptr;         // fp32 block output   [max_rows, H] (debug / TP partial)
+  __nv_bfloat16 *out_bf16 = nullptr;// e_agg_g             [max_rows, H]
+  moe::WorkItem *work1 = nullptr, *work2 = nullptr;
+  int *n_work = nullptr;            // [2]
+  int max_work1 = 0, max_work2 = 0;
+  unsigned int *status = nullptr;
+  CUtensorMap tm_x1, tm_x2;
+  int last_rows = 0;
+  long long launches = 0;
+  std::string err;
+};
+
+namespace moe {
+
+// route.cu
+void launch_router_logits(const __nv_bfloat16 *t, const __nv_bfloat16 *w3, const float *bias, float *logits,
+                          int T, int H, int E, cudaStream_t s);
+void launch_topk_softmax(const float *logits, int T, int E, int K, int *idx, float *w, int *counts,
+                         cudaStream_t s);
+void launch_build_index(const int *topk_idx, const int *counts, int T, int E, int K, int n_pairs1, int n_pairs2,
+                        int *offsets, int *pair_row, int *row_token, WorkItem *work1, WorkItem *work2,
+                        int *n_work, int max_work1, int max_work2, unsigned int *status, cudaStream_t s);
+void launch_gather_rows(const __nv_bfloat16 *t, const int *row_token, const int *offsets, int E, __half *xperm,
+                        int H, int max_pairs, cudaStream_t s);
+void launch_combine(const float *y, const int *topk_idx, const float *topk_w, const int *pair_row, int T, int H,
+                    int K, __nv_bfloat16 *out_bf16, float *out_f32, cudaStream_t s);
+
+// expert_gemm_sm100.cu
+cudaError_t expert_gemm_init();
+void launch_expert_gemm_mlp1(const CUtensorMap &tm_w, const CUtensorMap &tm_x, const GemmArgs &a, int grid,
+                             cudaStream_t s);
+void launch_expert_gemm_mlp2(const CUtensorMap &tm_w, const CUtensorMap &tm_x, const GemmArgs &a, int grid,
+                             cudaStream_t s);
+
+// expert_gemm_simt.cu (validation path)
+void launch_simt_mlp1(const uint8_t *codes, const uint8_t *scales_raw, const __nv_bfloat16 *bias, const __half *x,
+                      const int *offsets, int E, int H, int R1, __half *h_out, float limit, float alpha,
+                      int n_rows, cudaStream_t s);
+void launch_simt_mlp2(const uint8_t *codes, const uint8_t *scales_raw, const __nv_bfloat16 *bias, int add_bias,
+                      const __half *h, const int *offsets, int E, int Dl, int H, float *y_out, int n_rows,
+                      cudaStream_t s);
+
+}  // namespace moe

@@ -1,0 +1,351 @@
+// Routing side of the MoE block: router logits, top-k + softmax, expert
+// histogram, stable token->expert permutation, work list of the grouped GEMM,
+// row gather and the weighted un-permute.  Everything stays on the device: the
+// reference's per-layer host round trip (expert counts copied to the host, tile
+// maps built there, getp-csrc/getp_run.cpp:2648-2692 and :3019-3068) is replaced
+// by build_index_kernel.
+#include "moe_internal.cuh"
+
+namespace moe {
+
+// ---------------------------------------------------------------------------
+// Router logits: logits[t, e] = sum_k t[t, k] * Wr[e, k] + br[e], fp32.
+// Reference: matmul + bias of run.cpp:660-669 (double accumulation of float
+// products); the reference GPU path rounds the logits to bf16
+// (getp_run.cpp:2612-2620), which this kernel deliberately does not.
+//
+// The fp32 router weight is pre-split at load time into three bf16 planes
+// (hi + mid + lo == w exactly, 8+8+8 significand bits), so each plane times a
+// bf16 activation is an exact fp32 product and the sum runs on the tensor
+// cores (mma.sync m16n8k16, fp32 accumulate).  A block owns 16 tokens x 64
+// experts; its 8 warps split the k16 steps and their partial sums are added
+// in a fixed order in double precision.
+// ---------------------------------------------------------------------------
+constexpr int kRtTok = 16, kRtExp = 64, kRtWarps = 8;
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(kRtWarps * 32)
+router_logits_kernel(const __nv_bfloat16 *__restrict__ t, const __nv_bfloat16 *__restrict__ w3,
+                     const float *__restrict__ bias, float *__restrict__ logits, int T, int H, int E) {
+  __shared__ float part[kRtWarps][kRtTok][kRtExp + 1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, q = lane & 3;
+  const int tok0 = blockIdx.x * kRtTok, e0 = blockIdx.y * kRtExp;
+  const size_t plane = static_cast<size_t>(E) * H;
+
+  float acc[kRtExp / 8][4];
+#pragma unroll
+  for (int n = 0; n < kRtExp / 8; ++n)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
+
+  const int r0 = tok0 + g, r1 = tok0 + g + 8;
+  const uint32_t *x0 = reinterpret_cast<const uint32_t *>(t + static_cast<size_t>(min(r0, T - 1)) * H);
+  const uint32_t *x1 = reinterpret_cast<const uint32_t *>(t + static_cast<size_t>(min(r1, T - 1)) * H);
+  const bool v0 = r0 < T, v1 = r1 < T;
+
+  for (int ks = warp; ks < H / 16; ks += kRtWarps) {
+    const int kw = ks * 8 + q;  // 32-bit word index of (k0 + 2q)
+    uint32_t a[4];
+    a[0] = v0 ? __ldg(x0 + kw) : 0u;
+    a[1] = v1 ? __ldg(x1 + kw) : 0u;
+    a[2] = v0 ? __ldg(x0 + kw + 4) : 0u;
+    a[3] = v1 ? __ldg(x1 + kw + 4) : 0u;
+#pragma unroll
+    for (int n = 0; n < kRtExp / 8; ++n) {
+      const int e = e0 + n * 8 + g;
+      if (e0 + n * 8 >= E) break;
+      const bool ve = e < E;
+      const uint32_t *wrow = reinterpret_cast<const uint32_t *>(w3 + static_cast<size_t>(min(e, E - 1)) * H);
+#pragma unroll
+      for (int p = 0; p < 3; ++p) {
+        const uint32_t *wp = wrow + p * (plane / 2);
+        const uint32_t b0 = ve ? __ldg(wp + kw) : 0u;
+        const uint32_t b1 = ve ? __ldg(wp + kw + 4) : 0u;
+        mma_bf16_16816(acc[n], a, b0, b1);
+      }
+    }
+  }
+#pragma unroll
+  for (int n = 0; n < kRtExp / 8; ++n) {
+    part[warp][g][n * 8 + 2 * q] = acc[n][0];
+    part[warp][g][n * 8 + 2 * q + 1] = acc[n][1];
+    part[warp][g + 8][n * 8 + 2 * q] = acc[n][2];
+    part[warp][g + 8][n * 8 + 2 * q + 1] = acc[n][3];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < kRtTok * kRtExp; i += blockDim.x) {
+    const int r = i / kRtExp, c = i % kRtExp;
+    const int tok = tok0 + r, e = e0 + c;
+    if (tok >= T || e >= E) continue;
+    double s = 0.0;
+#pragma unroll
+    for (int w = 0; w < kRtWarps; ++w) s += static_cast<double>(part[w][r][c]);
+    float v = static_cast<float>(s);
+    v = __fadd_rn(v, bias[e]);  // run.cpp:667-669: bias added in float after the matmul
+    logits[static_cast<size_t>(tok) * E + e] = v;
+  }
+}
+
+void launch_router_logits(const __nv_bfloat16 *t, const __nv_bfloat16 *w3, const float *bias, float *logits,
+                          int T, int H, int E, cudaStream_t s) {
+  dim3 grid((T + kRtTok - 1) / kRtTok, (E + kRtExp - 1) / kRtExp);
+  router_logits_kernel<<<grid, kRtWarps * 32, 0, s>>>(t, w3, bias, logits, T, H, E);
+}
+
+// ---------------------------------------------------------------------------
+// Top-k + softmax over the selected logits + expert histogram.  One warp per
+// token.  Reference: topk (run.cpp:387-420) then softmax (run.cpp:335-353,
+// :674); GPU counterpart route_select_softmax_kernel_bf16io
+// (kernels/moe.hpp:465-561) and count_tokens_per_expert_kernel (:744).
+// Selection is exact: plain fp32 comparisons, equal values resolved towards
+// the lower index (kernels/moe.hpp:333-342).  Weights stay fp32.
+// ---------------------------------------------------------------------------
+constexpr int kMaxExpPerLane = 8;  // E <= 256
+constexpr int kMaxTopK = 8;
+
+__global__ void topk_softmax_kernel(const float *__restrict__ logits, int T, int E, int K, int *__restrict__ idx,
+                                    float *__restrict__ w, int *__restrict__ counts) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= T) return;
+  const float *row = logits + static_cast<size_t>(warp) * E;
+  float v[kMaxExpPerLane];
+  unsigned taken = 0;
+#pragma unroll
+  for (int i = 0; i < kMaxExpPerLane; ++i) {
+    const int e = lane + 32 * i;
+    v[i] = e < E ? row[e] : 0.f;
+    if (e >= E) taken |= 1u << i;
+  }
+  float sel_v = 0.f;  // lane k keeps the k-th selected logit
+  int sel_i = 0;
+  for (int k = 0; k < K; ++k) {
+    float bv = 0.f;
+    int bi = -1;
+#pragma unroll
+    for (int i = 0; i < kMaxExpPerLane; ++i) {
+      if (taken & (1u << i)) continue;
+      if (bi < 0 || v[i] > bv) { bv = v[i]; bi = lane + 32 * i; }  // ascending e: ties keep the lower index
+    }
+#pragma unroll
+    for (int off = 16; off; off >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+      if (oi >= 0 && (bi < 0 || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+    }
+    if (bi >= 0 && (bi & 31) == lane) taken |= 1u << (bi >> 5);
+    if (lane == k) { sel_v = bv; sel_i = bi; }
+  }
+  // softmax over the K selected values, double max/sum as in run.cpp:335-353
+  double mx = -1e300;
+  for (int k = 0; k < K; ++k) {
+    const float vk = __shfl_sync(0xffffffffu, sel_v, k);
+    mx = fmax(mx, static_cast<double>(vk));
+  }
+  float ex = 0.f;
+  if (lane < K) ex = expf(static_cast<float>(static_cast<double>(sel_v) - mx));
+  double sum = 0.0;
+  for (int k = 0; k < K; ++k) sum += static_cast<double>(__shfl_sync(0xffffffffu, ex, k));
+  if (lane < K) {
+    idx[static_cast<size_t>(warp) * K + lane] = sel_i;
+    w[static_cast<size_t>(warp) * K + lane] = static_cast<float>(static_cast<double>(ex) / sum);
+    if (counts != nullptr && sel_i >= 0) atomicAdd(&counts[sel_i], 1);
+  }
+}
+
+void launch_topk_softmax(const float *logits, int T, int E, int K, int *idx, float *w, int *counts,
+                         cudaStream_t s) {
+  const int threads = 128;
+  const int blocks = (T * 32 + threads - 1) / threads;
+  topk_softmax_kernel<<<blocks, threads, 0, s>>>(logits, T, E, K, idx, w, counts);
+}
+
+// ---------------------------------------------------------------------------
+// Offsets, stable compaction and the GEMM work lists.  One block per expert.
+// Reference: host scan + tile maps (getp_run.cpp:2648-2692) and
+// route_build_index_kernel_bf16wts (kernels/moe.hpp:1173-1270): rows of one
+// expert are in ascending token order.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ counts, int T, int E, int K,
+                   int n_pairs1, int n_pairs2, int *__restrict__ offsets, int *__restrict__ pair_row,
+                   int *__restrict__ row_token, WorkItem *__restrict__ work1, WorkItem *__restrict__ work2,
+                   int *__restrict__ n_work, int max_work1, int max_work2, unsigned int *status) {
+  __shared__ int s_red[2][8];
+  __shared__ int s_warp[8];
+  __shared__ int s_running;
+  const int e = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  // exclusive prefix over experts below e: rows and token tiles
+  int my_rows = 0, my_tiles = 0;
+  for (int i = tid; i < e; i += blockDim.x) {
+    const int c = counts[i];
+    my_rows += c;
+    my_tiles += (c + kTokTile - 1) / kTokTile;
+  }
+#pragma unroll
+  for (int off = 16; off; off >>= 1) {
+    my_rows += __shfl_xor_sync(0xffffffffu, my_rows, off);
+    my_tiles += __shfl_xor_sync(0xffffffffu, my_tiles, off);
+  }
+  if (lane == 0) { s_red[0][warp] = my_rows; s_red[1][warp] = my_tiles; }
+  if (tid == 0) s_running = 0;
+  __syncthreads();
+  int off = 0, tiles_before = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { off += s_red[0][i]; tiles_before += s_red[1][i]; }
+  const int cnt = counts[e];
+  if (tid == 0) {
+    offsets[e] = off;
+    if (e == E - 1) offsets[E] = off + cnt;
+  }
+
+  // stable compaction in ascending token order
+  for (int base = 0; base < T; base += blockDim.x) {
+    const int t = base + tid;
+    int hit = -1;
+    if (t < T)
+      for (int k = 0; k < K; ++k)
+        if (topk_idx[static_cast<size_t>(t) * K + k] == e) { hit = k; break; }
+    const unsigned m = __ballot_sync(0xffffffffu, hit >= 0);
+    if (lane == 0) s_warp[warp] = __popc(m);
+    __syncthreads();
+    int before = s_running;
+    for (int i = 0; i < warp; ++i) before += s_warp[i];
+    if (hit >= 0) {
+      const int r = off + before + __popc(m & ((1u << lane) - 1u));
+      if (before + __popc(m & ((1u << lane) - 1u)) < cnt) {
+        row_token[r] = t;
+        pair_row[static_cast<size_t>(t) * K + hit] = r;
+      } else {
+        atomicOr(status, ST_BAD_INDEX);
+      }
+    }
+    __syncthreads();
+    if (tid == 0) {
+      int tot = 0;
+      for (int i = 0; i < 8; ++i) tot += s_warp[i];
+      s_running += tot;
+    }
+    __syncthreads();
+  }
+  if (tid == 0 && s_running != cnt) atomicOr(status, ST_BAD_INDEX);
+
+  // work items: token tiles of at most kTokTile rows, evenly sized
+  const int ntt = (cnt + kTokTile - 1) / kTokTile;
+  const int ts = ntt ? (cnt + ntt - 1) / ntt : 0;
+  for (int which = 0; which < 2; ++which) {
+    const int np = which ? n_pairs2 : n_pairs1;
+    WorkItem *work = which ? work2 : work1;
+    const int cap = which ? max_work2 : max_work1;
+    const int start = tiles_before * np;
+    for (int i = tid; i < ntt * np; i += blockDim.x) {
+      const int pair = i / ntt, tt = i % ntt;
+      WorkItem it;
+      it.expert = e;
+      it.pair = pair;
+      it.row0 = off + tt * ts;
+      it.ntok = min(ts, cnt - tt * ts);
+      if (start + i < cap) work[start + i] = it;
+      else atomicOr(status, ST_BAD_INDEX);
+    }
+    if (e == E - 1 && tid == 0) n_work[which] = min((tiles_before + ntt) * np, cap);
+  }
+}
+
+void launch_build_index(const int *topk_idx, const int *counts, int T, int E, int K, int n_pairs1, int n_pairs2,
+                        int *offsets, int *pair_row, int *row_token, WorkItem *work1, WorkItem *work2,
+                        int *n_work, int max_work1, int max_work2, unsigned int *status, cudaStream_t s) {
+  build_index_kernel<<<E, 256, 0, s>>>(topk_idx, counts, T, E, K, n_pairs1, n_pairs2, offsets, pair_row,
+                                       row_token, work1, work2, n_work, max_work1, max_work2, status);
+}
+
+// ---------------------------------------------------------------------------
+// Row gather: xperm[r, :] = fp16(t[row_token[r], :]).  Reference:
+// pack_rows_kernel_bf16_in (kernels/moe.hpp:983-1048).  The GEMM operands are
+// fp16 (the MXFP4 decode instruction produces fp16); every bf16 value of
+// magnitude in [2^-14, 65504] converts exactly.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+gather_rows_kernel(const __nv_bfloat16 *__restrict__ t, const int *__restrict__ row_token,
+                   const int *__restrict__ offsets, int E, __half *__restrict__ xperm, int H) {
+  const int r = blockIdx.x;
+  if (r >= offsets[E]) return;
+  const int tok = row_token[r];
+  const uint4 *src = reinterpret_cast<const uint4 *>(t + static_cast<size_t>(tok) * H);
+  uint4 *dst = reinterpret_cast<uint4 *>(xperm + static_cast<size_t>(r) * H);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
+    const uint4 v = __ldg(src + i);
+    const uint32_t in[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float lo = __uint_as_float(in[j] << 16), hi = __uint_as_float(in[j] & 0xffff0000u);
+      const __half2 h = __floats2half2_rn(lo, hi);
+      o[j] = *reinterpret_cast<const uint32_t *>(&h);
+    }
+    dst[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+void launch_gather_rows(const __nv_bfloat16 *t, const int *row_token, const int *offsets, int E, __half *xperm,
+                        int H, int max_pairs, cudaStream_t s) {
+  gather_rows_kernel<<<max_pairs, 128, 0, s>>>(t, row_token, offsets, E, xperm, H);
+}
+
+// ---------------------------------------------------------------------------
+// Weighted un-permute: out[t, :] = sum_k w[t, k] * y[pair_row[t, k], :], terms
+// added in ascending expert index with separate multiply and add, which is the
+// order and rounding of run.cpp:678 / :738-741.  GPU counterpart:
+// reduce_tokenwise_expert_outputs_bf16_bf16wts (kernels/moe.hpp:700-730).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+combine_kernel(const float *__restrict__ y, const int *__restrict__ topk_idx, const float *__restrict__ topk_w,
+               const int *__restrict__ pair_row, int T, int H, int K, __nv_bfloat16 *__restrict__ out_bf16,
+               float *__restrict__ out_f32) {
+  const int t = blockIdx.x;
+  int ex[kMaxTopK], row[kMaxTopK];
+  float wt[kMaxTopK];
+  for (int k = 0; k < K; ++k) {
+    ex[k] = topk_idx[static_cast<size_t>(t) * K + k];
+    wt[k] = topk_w[static_cast<size_t>(t) * K + k];
+    row[k] = pair_row[static_cast<size_t>(t) * K + k];
+  }
+  for (int i = 1; i < K; ++i)  // insertion sort by expert index
+    for (int j = i; j > 0 && ex[j] < ex[j - 1]; --j) {
+      int a = ex[j]; ex[j] = ex[j - 1]; ex[j - 1] = a;
+      a = row[j]; row[j] = row[j - 1]; row[j - 1] = a;
+      float f = wt[j]; wt[j] = wt[j - 1]; wt[j - 1] = f;
+    }
+  for (int i = threadIdx.x; i < H / 4; i += blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < K; ++k) {
+      const float4 v = __ldg(reinterpret_cast<const float4 *>(y + static_cast<size_t>(row[k]) * H) + i);
+      acc.x = __fadd_rn(acc.x, __fmul_rn(v.x, wt[k]));
+      acc.y = __fadd_rn(acc.y, __fmul_rn(v.y, wt[k]));
+      acc.z = __fadd_rn(acc.z, __fmul_rn(v.z, wt[k]));
+      acc.w = __fadd_rn(acc.w, __fmul_rn(v.w, wt[k]));
+    }
+    if (out_f32 != nullptr) reinterpret_cast<float4 *>(out_f32 + static_cast<size_t>(t) * H)[i] = acc;
+    if (out_bf16 != nullptr) {
+      const __nv_bfloat162 a = __floats2bfloat162_rn(acc.x, acc.y), b = __floats2bfloat162_rn(acc.z, acc.w);
+      uint2 o;
+      o.x = *reinterpret_cast<const uint32_t *>(&a);
+      o.y = *reinterpret_cast<const uint32_t *>(&b);
+      reinterpret_cast<uint2 *>(out_bf16 + static_cast<size_t>(t) * H)[i] = o;
+    }
+  }
+}
+
+void launch_combine(const float *y, const int *topk_idx, const float *topk_w, const int *pair_row, int T, int H,
+                    int K, __nv_bfloat16 *out_bf16, float *out_f32, cudaStream_t s) {
+  combine_kernel<<<T, 256, 0, s>>>(y, topk_idx, topk_w, pair_row, T, H, K, out_bf16, out_f32);
+}
+
+}  // namespace moe

@@ -1,0 +1,133 @@
+/*
+ * C ABI of the B200 (sm_100a) tensor-parallel MXFP4 MoE block.
+ *
+ * This is the drop-in boundary for the MoE path of the reference runtime
+ * (getp-csrc/getp_run.cpp): the reference has no FFI layer, its boundary is the
+ * C++ call moe_gpu()/moe_gpu_120b() plus the weight loaders and the TP helpers.
+ * Each entry point below names the reference interface it replaces.  Plain
+ * pointers and sizes only; every function returns a status code (the reference
+ * prints and abort()s, getp-csrc/nccl.hpp:11-19) and never exits the process.
+ *
+ * Threading model as in the reference (getp_run.cpp:3514-3517): one host thread
+ * (or one process) per GPU; a handle is bound to one device and is used by one
+ * thread at a time.
+ */
+#ifndef MOE_B200_H
+#define MOE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct moe_ctx *moe_handle;
+
+enum {
+  MOE_OK = 0,
+  MOE_ERR_INVALID = 1,     /* bad argument or unsupported shape */
+  MOE_ERR_CUDA = 2,        /* a CUDA call failed; see moe_last_error() */
+  MOE_ERR_NOMEM = 3,
+  MOE_ERR_TIMEOUT = 4,     /* a bounded device- or host-side wait ran out */
+  MOE_ERR_SCALE_RANGE = 5, /* an E8M0 scale would push a weight out of fp16 range */
+  MOE_ERR_STATE = 6,       /* layer not loaded, peers not attached, ... */
+  MOE_ERR_NO_SM100 = 7     /* device is not compute capability 10.x */
+};
+
+/* moe_config.flags */
+#define MOE_CFG_KEEP_F32_OUT 1u /* also keep the fp32 block output for moe_get_debug() */
+
+/* Replaces Config (run.cpp:25-45, the fields the MoE block reads) plus the
+ * globals BATCH_SIZE / TENSOR_PARALLEL_SIZE (getp-csrc/config.hpp:3,11). */
+typedef struct moe_config {
+  int hidden_dim;        /* H, multiple of 32 */
+  int intermediate_dim;  /* D, multiple of 32 */
+  int n_experts;         /* E <= 256 */
+  int experts_per_token; /* K <= 8 */
+  int n_layers;
+  float swiglu_limit;    /* 7.0 */
+  float swiglu_alpha;    /* 1.702 */
+  int max_rows;          /* most rows one forward sees (the TP group's union batch) */
+  int tp_size;           /* ranks sharing the intermediate dimension; 1 = no TP */
+  int tp_rank;           /* rank_in_group (getp-csrc/nccl.hpp:30) */
+  int device;            /* CUDA ordinal this handle is bound to */
+  unsigned flags;        /* MOE_CFG_* */
+} moe_config;
+
+/* Replaces malloc_gpu_run_state* and malloc_gpu_weights_{20b,120b}
+ * (getp_run.cpp:588, :656): allocates every device buffer the block needs. */
+int moe_create(const moe_config *cfg, moe_handle *out);
+int moe_destroy(moe_handle h);
+
+/* Replaces copy_weights_to_gpu_{20b,120b} for the MoE tensors
+ * (getp_run.cpp:744, :1480).  HOST pointers to one layer's FULL tensors in the
+ * reference layout (GPUTransformerWeights, getp_run.cpp:48-81):
+ *   w1_codes  [E, 2D, H/2] u8, two e2m1 codes per byte, low nibble = even element
+ *   w1_scales [E, 2D, H/32] u8 E8M0, one per 32 elements along H
+ *   b1        [E, 2D] bf16            (rows 2j = gate_j, 2j+1 = up_j)
+ *   w2_codes  [E, H, D/2], w2_scales [E, H, D/32], b2 [E, H] bf16
+ *   router_w  [E, H] fp32, router_b [E] fp32
+ * With tp_size > 1 the rank's shard (mlp1_shard / mlp2_shard_input,
+ * getp_run.cpp:2488-2501, here on 32-element boundaries so that scale blocks
+ * are never split or re-quantised) is cut out inside. */
+int moe_load_layer(moe_handle h, int layer, const uint8_t *w1_codes, const uint8_t *w1_scales,
+                   const uint16_t *b1, const uint8_t *w2_codes, const uint8_t *w2_scales,
+                   const uint16_t *b2, const float *router_w, const float *router_b);
+
+/* The intermediate range [start, start+len) a rank owns; mirrors
+ * mlp2_shard_input (getp_run.cpp:2495-2501) with 32-aligned boundaries. */
+int moe_shard_range(int intermediate_dim, int tp_size, int tp_rank, int *start, int *len);
+
+/* moe_forward.flags */
+#define MOE_FWD_SIMT_GEMM 1u    /* run the plain CUDA-core validation GEMM instead of tcgen05 */
+#define MOE_FWD_PARTIAL_F32 2u  /* TP: leave this rank's fp32 partial in the handle, write no output */
+
+/* Replaces moe_gpu()/moe_gpu_120b() steps 2-8 (getp_run.cpp:2540, :2896): router,
+ * top-k + softmax, permutation, MLP1 + SwiGLU, MLP2, weighted combine, for `rows`
+ * already-normalised bf16 rows [rows, H] in DEVICE memory; writes bf16 [rows, H].
+ * Stream-ordered on `stream` (a cudaStream_t); no host synchronisation inside. */
+int moe_forward(moe_handle h, int layer, const void *t_dev, int rows, void *out_dev, unsigned flags,
+                void *stream);
+
+/* Same call for HOST buffers (pinned memory from moe_host_alloc copies
+ * asynchronously): host->device copy, the block, device->host copy, then waits
+ * and returns the device status. */
+int moe_forward_host(moe_handle h, int layer, const void *t_host, int rows, void *out_host, unsigned flags);
+
+/* Waits for the handle's stream work and reports MOE_ERR_TIMEOUT if any kernel
+ * recorded a bounded wait that ran out. */
+int moe_synchronize(moe_handle h);
+
+void *moe_host_alloc(size_t bytes);
+void moe_host_free(void *p);
+
+/* Stand-alone top-k + softmax over caller-supplied fp32 logits [rows, E] (device
+ * pointers).  Replaces run_route_select_softmax_fused (kernels/moe.hpp:565-599). */
+int moe_route_topk(moe_handle h, const float *logits_dev, int rows, int *idx_dev, float *w_dev, void *stream);
+
+/* Intermediate results of the last forward, copied to host memory. */
+enum {
+  MOE_DBG_LOGITS = 0,   /* f32 [rows, E]    router_score_g */
+  MOE_DBG_TOPK_IDX = 1, /* i32 [rows, K]    topk_i_g */
+  MOE_DBG_TOPK_W = 2,   /* f32 [rows, K]    topk_v_g */
+  MOE_DBG_COUNTS = 3,   /* i32 [E]          d_expert_counts */
+  MOE_DBG_OFFSETS = 4,  /* i32 [E+1]        d_expert_offsets */
+  MOE_DBG_PAIR_ROW = 5, /* i32 [rows, K]    local_ids_g */
+  MOE_DBG_ROW_TOKEN = 6,/* i32 [rows*K]     expert_row_token_g */
+  MOE_DBG_OUT_F32 = 7,  /* f32 [rows, H]    block output before the bf16 rounding (MOE_CFG_KEEP_F32_OUT) */
+  MOE_DBG_STATUS = 8,   /* u32 [1]          device status word */
+  MOE_DBG_HBUF = 9,     /* f16 [rows*K, Dl] SwiGLU output, permuted rows (gate_up_bf16_g) */
+  MOE_DBG_YBUF = 10     /* f32 [rows*K, H]  MLP2 output, permuted rows (expert_output_partial_g) */
+};
+int moe_get_debug(moe_handle h, int which, void *host_dst, size_t bytes);
+
+const char *moe_last_error(moe_handle h);
+const char *moe_strerror(int code);
+/* Number of kernels of this library launched by the handle so far. */
+long long moe_launch_count(moe_handle h);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
