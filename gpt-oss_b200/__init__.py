@@ -16,7 +16,8 @@ import numpy as np
 from . import synth  # noqa: F401  (re-exported for tests and bench)
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libmoe_b200.so")
+# MOE_B200_LIB selects another build of the same library (e.g. one compiled with extra flags).
+LIB_PATH = os.environ.get("MOE_B200_LIB") or os.path.join(HERE, "libmoe_b200.so")
 
 MOE_OK = 0
 ERR_NAMES = {1: "INVALID", 2: "CUDA", 3: "NOMEM", 4: "TIMEOUT", 5: "SCALE_RANGE", 6: "STATE", 7: "NO_SM100"}
@@ -31,8 +32,9 @@ DBG_LOGITS, DBG_TOPK_IDX, DBG_TOPK_W, DBG_COUNTS, DBG_OFFSETS, DBG_PAIR_ROW, DBG
 EXPORTS = [
     "moe_create", "moe_destroy", "moe_load_layer", "moe_shard_range", "moe_forward", "moe_forward_host",
     "moe_synchronize", "moe_host_alloc", "moe_host_free", "moe_route_topk", "moe_get_debug",
-    "moe_last_error", "moe_strerror", "moe_launch_count",
+    "moe_last_error", "moe_strerror", "moe_launch_count", "moe_profile_enable", "moe_profile_collect",
 ]
+STAGES = ("router", "topk", "index", "gather", "mlp1", "mlp2", "combine")
 
 
 class MoeConfig(C.Structure):
@@ -77,6 +79,8 @@ def lib() -> C.CDLL:
         L.moe_strerror.restype = C.c_char_p
         L.moe_launch_count.argtypes = [C.c_void_p]
         L.moe_launch_count.restype = C.c_longlong
+        L.moe_profile_enable.argtypes = [C.c_void_p, C.c_int]
+        L.moe_profile_collect.argtypes = [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_int)]
         _lib = L
     return _lib
 
@@ -176,11 +180,20 @@ class MoeBlock:
             DBG_LOGITS: ((T, E), np.float32), DBG_TOPK_IDX: ((T, K), np.int32), DBG_TOPK_W: ((T, K), np.float32),
             DBG_COUNTS: ((E,), np.int32), DBG_OFFSETS: ((E + 1,), np.int32), DBG_PAIR_ROW: ((T, K), np.int32),
             DBG_ROW_TOKEN: ((T * K,), np.int32), DBG_OUT_F32: ((T, H), np.float32),
-            DBG_STATUS: ((1,), np.uint32), DBG_HBUF: ((T * K, self.Dl), np.float16),
-            DBG_YBUF: ((T * K, H), np.float32)}[which]
+            DBG_STATUS: ((1,), np.uint32), DBG_YBUF: ((T * K, H), np.float32)}[which]
         out = np.empty(shape, dtype=dt)
         self._check(self.L.moe_get_debug(self.h, which, out.ctypes.data_as(C.c_void_p), out.nbytes))
         return out
+
+    def profile(self, on: bool):
+        self._check(self.L.moe_profile_enable(self.h, int(on)))
+
+    def profile_collect(self) -> tuple[dict, int]:
+        """Summed milliseconds per stage and the number of profiled calls."""
+        ms = (C.c_float * len(STAGES))()
+        n = C.c_int()
+        self._check(self.L.moe_profile_collect(self.h, ms, C.byref(n)))
+        return {k: float(ms[i]) for i, k in enumerate(STAGES)}, n.value
 
     def launches(self) -> int:
         return int(self.L.moe_launch_count(self.h))

@@ -1,9 +1,8 @@
 // Validation path of the two expert GEMMs on plain CUDA cores (one warp per
-// output element, fp32 accumulation).  It shares the MXFP4 decode routine with
-// the tensor-core kernel and exists to tell a decode/layout error from a
-// tcgen05 pipeline error on the device; moe_forward runs it only when
-// MOE_FWD_SIMT_GEMM is passed.  Same arithmetic contract as the tensor-core
-// path: fp16 operands, fp32 accumulate, fp16 SwiGLU output, fp32 MLP2 output.
+// output element, fp32 accumulation, fp16 operands decoded with cvt.e2m1x2).
+// It shares nothing with the tensor-core kernel but the packed weights, and
+// exists to tell a weight-layout error from a tcgen05 pipeline error on the
+// device; moe_forward runs it only when MOE_FWD_SIMT_GEMM is passed.
 #include "moe_internal.cuh"
 #include "sm100_ptx.cuh"
 #include "swiglu.cuh"
@@ -47,7 +46,7 @@ __device__ __forceinline__ float warp_dot_mxfp4(const uint8_t *codes, const uint
 }
 
 __global__ void __launch_bounds__(256)
-simt_mlp1_kernel(const uint8_t *__restrict__ codes, const uint8_t *__restrict__ scales,
+simt_mlp1_kernel(const uint8_t *__restrict__ codes, int pitch, const uint8_t *__restrict__ scales,
                  const __nv_bfloat16 *__restrict__ bias, const __half *__restrict__ x,
                  const int *__restrict__ offsets, int E, int H, int R1, __half *__restrict__ h_out, float limit,
                  float alpha) {
@@ -60,8 +59,8 @@ simt_mlp1_kernel(const uint8_t *__restrict__ codes, const uint8_t *__restrict__ 
   const int e = expert_of_row(offsets, E, r);
   const size_t row_g = static_cast<size_t>(e) * R1 + 2 * j;
   const __half *xr = x + static_cast<size_t>(r) * H;
-  float g = warp_dot_mxfp4(codes + row_g * (H / 2), scales + row_g * (H / 32), xr, H, lane);
-  float u = warp_dot_mxfp4(codes + (row_g + 1) * (H / 2), scales + (row_g + 1) * (H / 32), xr, H, lane);
+  float g = warp_dot_mxfp4(codes + row_g * pitch, scales + row_g * (H / 32), xr, H, lane);
+  float u = warp_dot_mxfp4(codes + (row_g + 1) * pitch, scales + (row_g + 1) * (H / 32), xr, H, lane);
   if (lane == 0) {
     g += __bfloat162float(bias[row_g]);
     u += __bfloat162float(bias[row_g + 1]);
@@ -70,7 +69,7 @@ simt_mlp1_kernel(const uint8_t *__restrict__ codes, const uint8_t *__restrict__ 
 }
 
 __global__ void __launch_bounds__(256)
-simt_mlp2_kernel(const uint8_t *__restrict__ codes, const uint8_t *__restrict__ scales,
+simt_mlp2_kernel(const uint8_t *__restrict__ codes, int pitch, const uint8_t *__restrict__ scales,
                  const __nv_bfloat16 *__restrict__ bias, int add_bias, const __half *__restrict__ h,
                  const int *__restrict__ offsets, int E, int Dl, int H, float *__restrict__ y_out) {
   const int r = blockIdx.x;
@@ -80,26 +79,25 @@ simt_mlp2_kernel(const uint8_t *__restrict__ codes, const uint8_t *__restrict__ 
   if (i >= H) return;
   const int e = expert_of_row(offsets, E, r);
   const size_t row = static_cast<size_t>(e) * H + i;
-  float v = warp_dot_mxfp4(codes + row * (Dl / 2), scales + row * (Dl / 32), h + static_cast<size_t>(r) * Dl, Dl,
-                           lane);
+  float v = warp_dot_mxfp4(codes + row * pitch, scales + row * (Dl / 32), h + static_cast<size_t>(r) * Dl, Dl, lane);
   if (lane == 0) {
     if (add_bias) v += __bfloat162float(bias[row]);
     y_out[static_cast<size_t>(r) * H + i] = v;
   }
 }
 
-void launch_simt_mlp1(const uint8_t *codes, const uint8_t *scales_raw, const __nv_bfloat16 *bias, const __half *x,
-                      const int *offsets, int E, int H, int R1, __half *h_out, float limit, float alpha,
-                      int n_rows, cudaStream_t s) {
+void launch_simt_mlp1(const uint8_t *codes, int pitch, const uint8_t *scales_raw, const __nv_bfloat16 *bias,
+                      const __half *x, const int *offsets, int E, int H, int R1, __half *h_out, float limit,
+                      float alpha, int n_rows, cudaStream_t s) {
   dim3 grid(n_rows, (R1 / 2 + 7) / 8);
-  simt_mlp1_kernel<<<grid, 256, 0, s>>>(codes, scales_raw, bias, x, offsets, E, H, R1, h_out, limit, alpha);
+  simt_mlp1_kernel<<<grid, 256, 0, s>>>(codes, pitch, scales_raw, bias, x, offsets, E, H, R1, h_out, limit, alpha);
 }
 
-void launch_simt_mlp2(const uint8_t *codes, const uint8_t *scales_raw, const __nv_bfloat16 *bias, int add_bias,
-                      const __half *h, const int *offsets, int E, int Dl, int H, float *y_out, int n_rows,
-                      cudaStream_t s) {
+void launch_simt_mlp2(const uint8_t *codes, int pitch, const uint8_t *scales_raw, const __nv_bfloat16 *bias,
+                      int add_bias, const __half *h, const int *offsets, int E, int Dl, int H, float *y_out,
+                      int n_rows, cudaStream_t s) {
   dim3 grid(n_rows, (H + 7) / 8);
-  simt_mlp2_kernel<<<grid, 256, 0, s>>>(codes, scales_raw, bias, add_bias, h, offsets, E, Dl, H, y_out);
+  simt_mlp2_kernel<<<grid, 256, 0, s>>>(codes, pitch, scales_raw, bias, add_bias, h, offsets, E, Dl, H, y_out);
 }
 
 }  // namespace moe

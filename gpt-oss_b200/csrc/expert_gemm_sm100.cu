@@ -1,33 +1,35 @@
-// Grouped expert GEMM for sm_100a: MXFP4 weights x fp16 activations on the
-// tcgen05 tensor cores, for MLP1 (+bias, clamped SwiGLU) and MLP2 (+bias).
+// Grouped expert GEMM for sm_100a: block-scaled tcgen05 MMA (kind::mxf8f6f4)
+// that consumes the MXFP4 expert weights exactly as they lie in HBM, for MLP1
+// (+bias, clamped SwiGLU) and MLP2 (+bias).
 //
 // Reference counterparts: grouped_mlp1_bf16_bias_kernel_tiled_optimized_outbf16
 // and grouped_mlp2_... (getp-csrc/kernels/moe.hpp:2651, :2923, :3197) with
 // swiglu_epilogue_kernel_bf16_mlp_in_bf16 (:1472) between them, fed by weights
 // that the reference first expands to bf16 in a staging buffer
-// (getp_run.cpp:1019-1086).  Here the packed 4-bit weights are the only copy in
-// HBM and are decoded on the way to the tensor cores.
+// (getp_run.cpp:1019-1086).  Here the packed 4-bit codes and their E8M0 scales
+// go from HBM through TMA straight into the tensor core; no thread touches a
+// weight.
 //
-// Shape of the computation ("swap-AB"): per work item (expert e, 256 weight
-// rows, <= 96 token rows) the kernel forms D[n, tok] = sum_k W[e][n][k] * X[tok][k]
-// with the WEIGHT rows on the MMA M axis (two M = 128 tiles) and the tokens on
-// the N axis, so a decode-sized token count (tens of rows per expert) fills the
-// tensor core and every weight byte is read and decoded once per token tile.
+// Why this shape.  On this part a tcgen05.mma costs the same ~0.1 us whatever
+// its M (64/128) and N (16..256), so what counts is MACs per instruction:
+// weights go on the N axis (240 rows per work item; 240 divides both 5760 and
+// 2880) and the tokens of one expert on the M = 128 axis.  There is no
+// bf16 x fp4 instruction, so every bf16 activation is split into two e4m3 terms
+// (high + low, exact for bf16 inputs): a token tile is 64 tokens = 128 rows,
+// row 2i the high term of token i, row 2i+1 its low term whose block scale
+// carries the extra 2^-4.  The two partial sums land in adjacent lanes of the
+// accumulator and are added in the epilogue.
 //
-// Data flow per 128-element slice of k (one shared-memory stage):
-//   TMA  : packed codes  [256 rows x 64 B]  (64-byte swizzle)         -> smem
-//          E8M0 scales   [256 rows x 4]     (pre-tiled at load time)   -> smem
-//          activations   [<=96 rows x 128 fp16] as two 64-wide K-major
-//                        tiles (128-byte swizzle)                      -> smem
-//   dequant warps (8): one weight row per thread, cvt.e2m1x2 -> fp16 pairs,
-//          times 2^scale, tcgen05.st into a tensor-memory A buffer (64 k wide)
-//   MMA thread: tcgen05.mma kind::f16, A from tensor memory, B from smem,
-//          fp32 accumulators in tensor memory (double buffered across items)
-//   epilogue warps (4): tcgen05.ld, bias, SwiGLU (MLP1) and store.
-//
-// Tensor memory map (512 columns): [0,384) two accumulator buffers of
-// 2 tiles x 96 columns; [384,512) two A buffers of 2 tiles x 32 columns.
+// Per 128-element slice of k (one shared-memory stage) the producer thread
+// issues: weight codes [240 rows x 128] (TMA, 16U4_ALIGN16B: 4-bit codes are
+// expanded to the 8-bit containers the MMA reads, 128-byte swizzle), weight
+// scales (two 512-byte atoms, pre-tiled at load time), activations [128 rows x
+// 128] e4m3 (TMA, 128-byte swizzle).  The MMA thread copies the scale atoms to
+// tensor memory (tcgen05.cp) and issues four K = 32 instructions.  Four
+// epilogue warps drain the fp32 accumulator (double buffered: 2 x 240 columns).
 // No cluster launch, no multicast: every CTA fetches its own tiles.
+#include <cuda_fp8.h>
+
 #include "moe_internal.cuh"
 #include "sm100_ptx.cuh"
 #include "swiglu.cuh"
@@ -36,54 +38,64 @@ namespace moe {
 
 using namespace sm100;
 
-constexpr int kStages = 5;
-constexpr int kWBytes = kPairRows * (kChunkK / 2);        // 16384
-constexpr int kXHalfBytes = kTokTile * 128;               // 12288: 96 rows x 64 fp16
-constexpr int kXBytes = 2 * kXHalfBytes;                  // 24576
-constexpr int kStageBytes = kWBytes + kXBytes + kScaleChunkBytes;  // 41984
-constexpr int kXBoxBytes = kXBoxRows * 128;               // 4096
-constexpr int kNumBars = 2 * kStages + 8;
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*alignment slack*/ + 256 /*barriers etc.*/;
+constexpr int kStages = 4;
+constexpr int kABytes = kTileM * kChunkK;         // 16384: 128 rows x 128 e4m3
+constexpr int kWBytes = kTileNPad * kChunkK;      // 32768: 256 rows x 128 containers (240 loaded)
+// the transaction count of a 16U4_ALIGN16B copy is the PACKED size: 240 rows x 64 bytes
+constexpr int kWLoadBytes = kTileN * kChunkK / 2; // 15360
+constexpr int kStageBytes = kABytes + kWBytes + kSfbChunkBytes;  // 50176
+constexpr int kSfaOff = kStages * kStageBytes;    // two per-item activation scale atoms
+constexpr int kBarOff = kSfaOff + 2 * kSfAtomBytes;
+constexpr int kNumBars = 2 * kStages + 6;         // full, empty, d_full[2], d_empty[2], sfa_full[2]
+constexpr int kSmemBytes = kBarOff + 8 * kNumBars + 16 + 1024 /*alignment slack*/;
 
-constexpr int kEpiWarps = 4, kDqWarps = 8;
-constexpr int kProducerWarp = kEpiWarps + kDqWarps;  // 12
-constexpr int kMmaWarp = kProducerWarp + 1;          // 13
-constexpr int kThreads = (kMmaWarp + 1) * 32;        // 448
+constexpr int kEpiWarps = 4;
+constexpr int kProducerWarp = 4, kMmaWarp = 5;
+constexpr int kThreads = 6 * 32;
 
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kAccCol0 = 0, kAccBufCols = 2 * kTokTile /*192*/, kAccTileCols = kTokTile;
-constexpr uint32_t kACol0 = 384, kABufCols = 64, kATileCols = 32;
+constexpr uint32_t kAccBufCols = kTileN;          // accumulator buffer d at columns d*240
+constexpr uint32_t kSfaCol0 = 480;                // + 4*(item & 1)
+constexpr uint32_t kSfbCol0 = 488;                // + 8*(chunk & 1)
 
 static_assert(kStageBytes % 1024 == 0, "stages must keep 1024-byte alignment for the swizzled tiles");
 static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 
-template <int MODE>  // 1 = MLP1 (bias + SwiGLU -> fp16), 2 = MLP2 (bias -> fp32)
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+__device__ __forceinline__ float e4m3_to_float(uint32_t byte) {
+  const __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(byte), __NV_E4M3);
+  return __half2float(*reinterpret_cast<const __half *>(&h));
+}
+
+template <int MODE>  // 1 = MLP1 (bias + SwiGLU -> e4m3 high/low rows), 2 = MLP2 (bias -> fp32)
 __global__ void __launch_bounds__(kThreads, 1)
 expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                    const GemmArgs p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t bar_base = smem_base + kStages * kStageBytes;
-  volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem_gen + kStages * kStageBytes + 8 * kNumBars);
+  const uint32_t bar_base = smem_base + kBarOff;
+  volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem_gen + kBarOff + 8 * kNumBars);
   uint32_t *tmem_slot = const_cast<uint32_t *>(abort_flag) + 1;
 
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
-  auto aready_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
-  auto afree_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
-  auto dfull_bar = [&](int d) { return bar_base + 8u * (2 * kStages + 4 + d); };
-  auto dempty_bar = [&](int d) { return bar_base + 8u * (2 * kStages + 6 + d); };
+  auto dfull_bar = [&](int d) { return bar_base + 8u * (2 * kStages + d); };
+  auto dempty_bar = [&](int d) { return bar_base + 8u * (2 * kStages + 2 + d); };
+  auto sfa_bar = [&](int d) { return bar_base + 8u * (2 * kStages + 4 + d); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int a = 0; a < 2; ++a) {
-      mbar_init(aready_bar(a), kDqWarps);
-      mbar_init(afree_bar(a), 1);
-      mbar_init(dfull_bar(a), 1);
-      mbar_init(dempty_bar(a), kEpiWarps);
+    for (int d = 0; d < 2; ++d) {
+      mbar_init(dfull_bar(d), 1);
+      mbar_init(dempty_bar(d), kEpiWarps);
+      mbar_init(sfa_bar(d), 1);
     }
     *abort_flag = 0u;
     fence_mbar_init();
@@ -109,25 +121,27 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------- TMA producer
     if (lane == 0) {
-      uint32_t it = 0;
+      uint32_t it = 0, item = 0;
       bool ok = true;
-      for (int wi = blockIdx.x; ok && wi < n_work; wi += gridDim.x) {
+      for (int wi = blockIdx.x; ok && wi < n_work; wi += gridDim.x, ++item) {
         const WorkItem w = p.work[wi];
-        const int nbox = (w.ntok + kXBoxRows - 1) / kXBoxRows;
-        const uint8_t *sc_src = p.scales + (static_cast<size_t>(w.expert) * p.n_pairs + w.pair) * nkc * kScaleChunkBytes;
+        // activation scale atom of this token tile; its slot is free once the MMAs of item-2 are done,
+        // which the accumulator hand-over of that item (d_empty) has already implied
+        const uint32_t d = item & 1u;
+        if (!mbar_wait(dempty_bar(d), ((item >> 1) & 1u) ^ 1u, abort_flag, p.status, ST_WAIT_DEMPTY)) { ok = false; break; }
+        mbar_arrive_expect_tx(sfa_bar(d), kSfAtomBytes);
+        bulk_load(smem_base + kSfaOff + d * kSfAtomBytes, p.sfa + static_cast<size_t>(w.tile) * p.sfa_tile_stride,
+                  kSfAtomBytes, sfa_bar(d));
+        const uint8_t *sfb_src = p.sfb + (static_cast<size_t>(w.expert) * p.n_ntiles + w.ntile) * nkc * kSfbChunkBytes;
         for (int kc = 0; kc < nkc; ++kc, ++it) {
           const int s = it % kStages;
           if (!mbar_wait(empty_bar(s), ((it / kStages) & 1u) ^ 1u, abort_flag, p.status, ST_WAIT_EMPTY)) { ok = false; break; }
-          const int k0 = kc * kChunkK;
-          const int nhalf = (K - k0 > kSubK) ? 2 : 1;
           const uint32_t stage = smem_base + s * kStageBytes;
-          mbar_arrive_expect_tx(full_bar(s), kWBytes + kScaleChunkBytes + nhalf * nbox * kXBoxBytes);
-          tma_load_3d(stage, &tm_w, k0 / 2, w.pair * kPairRows, w.expert, full_bar(s));
-          bulk_load(stage + kWBytes + kXBytes, sc_src + static_cast<size_t>(kc) * kScaleChunkBytes, kScaleChunkBytes, full_bar(s));
-          for (int h = 0; h < nhalf; ++h)
-            for (int b = 0; b < nbox; ++b)
-              tma_load_2d(stage + kWBytes + h * kXHalfBytes + b * kXBoxBytes, &tm_x, k0 + h * kSubK,
-                          w.row0 + b * kXBoxRows, full_bar(s));
+          mbar_arrive_expect_tx(full_bar(s), kABytes + kWLoadBytes + kSfbChunkBytes);
+          tma_load_2d(stage, &tm_x, kc * kChunkK, w.tile * kTileM, full_bar(s));
+          tma_load_3d(stage + kABytes, &tm_w, kc * kChunkK, w.ntile * kTileN, w.expert, full_bar(s));
+          bulk_load(stage + kABytes + kWBytes, sfb_src + static_cast<size_t>(kc) * kSfbChunkBytes, kSfbChunkBytes,
+                    full_bar(s));
         }
       }
       if (!ok) {  // give copies in flight time to land before the CTA's shared memory is released
@@ -140,118 +154,99 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       uint32_t it = 0, item = 0;
       bool ok = true;
       for (int wi = blockIdx.x; ok && wi < n_work; wi += gridDim.x, ++item) {
-        const WorkItem w = p.work[wi];
-        const int nmma = (w.ntok + 15) & ~15;
-        const int ntiles = (w.pair * kPairRows + kTileRows < p.R) ? 2 : 1;
-        const uint32_t idesc = idesc_f16_m128(nmma);
         const uint32_t d = item & 1u;
         if (!mbar_wait(dempty_bar(d), ((item >> 1) & 1u) ^ 1u, abort_flag, p.status, ST_WAIT_DEMPTY)) { ok = false; break; }
+        if (!mbar_wait(sfa_bar(d), (item >> 1) & 1u, abort_flag, p.status, ST_WAIT_AREADY)) { ok = false; break; }
         tc_fence_after();
+        const uint32_t sfa_t = tmem_base + kSfaCol0 + 4 * d;
+        tmem_cp_sf_atom(sfa_t, smem_base + kSfaOff + d * kSfAtomBytes);
+        const uint32_t d_addr = tmem_base + d * kAccBufCols;
         for (int kc = 0; ok && kc < nkc; ++kc, ++it) {
           const int s = it % kStages;
           if (!mbar_wait(full_bar(s), (it / kStages) & 1u, abort_flag, p.status, ST_WAIT_FULL)) { ok = false; break; }
-          const uint32_t xbase = smem_base + s * kStageBytes + kWBytes;
-          const int krem = K - kc * kChunkK;
-          for (int h = 0; h < 2; ++h) {
-            if (!mbar_wait(aready_bar(h), it & 1u, abort_flag, p.status, ST_WAIT_AREADY)) { ok = false; break; }
-            tc_fence_after();
-            const int ksteps = max(0, min(4, (krem - h * kSubK) / 16));
-            for (int t = 0; t < ntiles; ++t) {
-              const uint32_t d_addr = tmem_base + kAccCol0 + d * kAccBufCols + t * kAccTileCols;
-              const uint32_t a_addr = tmem_base + kACol0 + h * kABufCols + t * kATileCols;
-              for (int j = 0; j < ksteps; ++j) {
-                const uint64_t bdesc = smem_desc_sw128(xbase + h * kXHalfBytes + j * 32);
-                mma_f16_ts(d_addr, a_addr + j * 8, bdesc, idesc, (kc | h | j) != 0);
-              }
-            }
-            mma_commit(afree_bar(h));
+          tc_fence_after();
+          const uint32_t stage = smem_base + s * kStageBytes;
+          const uint32_t sfb_t = tmem_base + kSfbCol0 + 8 * (it & 1u);
+          tmem_cp_sf_atom(sfb_t, stage + kABytes + kWBytes);
+          tmem_cp_sf_atom(sfb_t + 4, stage + kABytes + kWBytes + kSfAtomBytes);
+          const int ksteps = min(4, (K - kc * kChunkK) / 32);
+          for (int kb = 0; kb < ksteps; ++kb) {
+            const uint64_t adesc = smem_desc_sw128(stage + kb * 32);
+            const uint64_t bdesc = smem_desc_sw128(stage + kABytes + kb * 32);
+            mma_mxf8f6f4_ss(d_addr, adesc, bdesc, idesc_mxf8f6f4_m128(kTileN, kb), (kc | kb) != 0, sfa_t, sfb_t);
           }
-          if (ok) mma_commit(empty_bar(s));
+          mma_commit(empty_bar(s));
         }
         if (ok) mma_commit(dfull_bar(d));
       }
     }
-  } else if (warp >= kEpiWarps) {
-    // ------------------------------------------------------------- dequant warps
-    const int dq = warp - kEpiWarps;
-    const int tile = dq >> 2, quad = warp & 3;
-    const int rb = tile * kTileRows + quad * 32 + lane;  // row inside the 256-row box
-    const uint32_t sw = static_cast<uint32_t>((rb >> 1) & 3);
-    const uint32_t lane_field = static_cast<uint32_t>(quad * 32) << 16;
-    uint32_t it = 0;
-    bool ok = true;
-    for (int wi = blockIdx.x; ok && wi < n_work; wi += gridDim.x) {
-      const WorkItem w = p.work[wi];
-      const bool active = tile == 0 || (w.pair * kPairRows + kTileRows < p.R);
-      for (int kc = 0; ok && kc < nkc; ++kc, ++it) {
-        const int s = it % kStages;
-        if (!mbar_wait(full_bar(s), (it / kStages) & 1u, abort_flag, p.status, ST_WAIT_FULL)) { ok = false; break; }
-        const uint8_t *stage = smem_gen + s * kStageBytes;
-        const uint32_t sc4 = *reinterpret_cast<const uint32_t *>(stage + kWBytes + kXBytes + rb * 4);
-        const int krem = K - kc * kChunkK;
-        for (int h = 0; h < 2; ++h) {
-          if (!mbar_wait(afree_bar(h), (it & 1u) ^ 1u, abort_flag, p.status, ST_WAIT_AFREE)) { ok = false; break; }
-          tc_fence_after();
-          const int nblk = max(0, min(2, (krem - h * kSubK) / 32));
-          if (active) {
-            for (int c = 0; c < nblk; ++c) {
-              const uint32_t c16 = 2u * h + c;
-              const uint4 codes = *reinterpret_cast<const uint4 *>(stage + rb * 64 + ((c16 ^ sw) << 4));
-              uint32_t regs[16];
-              dequant_block32(codes, e8m0_to_f16x2((sc4 >> (8 * c16)) & 0xffu), regs);
-              tmem_st16(tmem_base + lane_field + kACol0 + h * kABufCols + tile * kATileCols + c * 16, regs);
-            }
-            tmem_wait_st();
-          }
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(aready_bar(h));
-        }
-      }
-    }
   } else {
     // ------------------------------------------------------------- epilogue warps
-    const int quad = warp;  // warps 0..3 <-> TMEM lanes 32*warp..
+    // lane l of warp q holds accumulator row 32q + l: token 16q + l/2, high (even l) or low (odd l) term
+    const int quad = warp;
     const uint32_t lane_field = static_cast<uint32_t>(quad * 32) << 16;
+    const int odd = lane & 1;
+    const int tok = quad * 16 + (lane >> 1);
+    const float h_scale = exp2f(static_cast<float>(-p.h_exp));
     uint32_t item = 0;
     bool ok = true;
     for (int wi = blockIdx.x; ok && wi < n_work; wi += gridDim.x, ++item) {
       const WorkItem w = p.work[wi];
-      const int nmma = (w.ntok + 15) & ~15;
-      const int ntiles = (w.pair * kPairRows + kTileRows < p.R) ? 2 : 1;
       const uint32_t d = item & 1u;
       if (!mbar_wait(dfull_bar(d), (item >> 1) & 1u, abort_flag, p.status, ST_WAIT_DFULL)) { ok = false; break; }
       tc_fence_after();
-      for (int t = 0; t < ntiles; ++t) {
-        const int n_loc = w.pair * kPairRows + t * kTileRows + quad * 32 + lane;
-        const bool row_ok = n_loc < p.R;
-        float bias = 0.f;
-        if (row_ok && p.add_bias) bias = __bfloat162float(p.bias[static_cast<size_t>(w.expert) * p.R + n_loc]);
-        for (int c0 = 0; c0 < nmma; c0 += 16) {
-          uint32_t v[16];
-          tmem_ld16(tmem_base + lane_field + kAccCol0 + d * kAccBufCols + t * kAccTileCols + c0, v);
-          tmem_wait_ld();
-          if (MODE == 1) {
-            const int odd = lane & 1;
+      const int n0 = w.ntile * kTileN;
+      const bool tok_ok = tok < w.ntok;
+      const __nv_bfloat16 *bias_row = p.bias + static_cast<size_t>(w.expert) * p.R;
+      for (int c0 = 0; c0 < kTileN; c0 += 16) {
+        if (n0 + c0 >= p.R) break;  // uniform: rows past the matrix (zero-filled) produce nothing
+        uint32_t v[16];
+        tmem_ld16(tmem_base + lane_field + d * kAccBufCols + c0, v);
+        tmem_wait_ld();
+        // sum of the high and low partial products; afterwards even lanes own columns 0-7, odd lanes 8-15
+        float tot[8];
 #pragma unroll
-            for (int i = 0; i < 16; i += 2) {
-              const float f0 = __uint_as_float(v[i]) + bias, f1 = __uint_as_float(v[i + 1]) + bias;
-              const float send = odd ? f0 : f1;
-              const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
-              const float gate = odd ? recv : f0;
-              const float up = odd ? f1 : recv;
-              const int tok = c0 + i + odd;
-              const float hv = swiglu_clamped(gate, up, p.limit, p.alpha);
-              if (row_ok && tok < w.ntok)
-                p.h_out[static_cast<size_t>(w.row0 + tok) * p.ld_out + (n_loc >> 1)] = __float2half_rn(hv);
-            }
-          } else {
+        for (int i = 0; i < 8; ++i) {
+          const float first = __uint_as_float(v[i]), second = __uint_as_float(v[8 + i]);
+          const float mine = odd ? second : first;
+          const float give = odd ? first : second;
+          tot[i] = mine + __shfl_xor_sync(0xffffffffu, give, 1);
+        }
+        const int nc = n0 + c0 + 8 * odd;  // first of this lane's 8 columns
+        float b[8];
+        if (p.add_bias && nc < p.R) {
+          const uint4 bv = __ldg(reinterpret_cast<const uint4 *>(bias_row + nc));
+          const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const int tok = c0 + i;
-              if (row_ok && tok < w.ntok)
-                p.y_out[static_cast<size_t>(w.row0 + tok) * p.ld_out + n_loc] = __uint_as_float(v[i]) + bias;
-            }
+          for (int i = 0; i < 4; ++i) {
+            b[2 * i] = __uint_as_float(bw[i] << 16);
+            b[2 * i + 1] = __uint_as_float(bw[i] & 0xffff0000u);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) b[i] = 0.f;
+        }
+        if (MODE == 1) {
+          float hs[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            hs[i] = swiglu_clamped(tot[2 * i] + b[2 * i], tot[2 * i + 1] + b[2 * i + 1], p.limit, p.alpha) * h_scale;
+          const uint32_t hi4 = pack_e4m3x4(hs[0], hs[1], hs[2], hs[3]);
+          float r[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) r[i] = (hs[i] - e4m3_to_float((hi4 >> (8 * i)) & 0xffu)) * 16.0f;
+          const uint32_t lo4 = pack_e4m3x4(r[0], r[1], r[2], r[3]);
+          const int j = nc >> 1;  // this lane's 4 intermediate features j .. j+3
+          if (tok_ok && nc < p.R) {
+            uint8_t *dst = p.hq_out + (static_cast<size_t>(w.tile) * kTileM + 2 * tok) * p.ld_out + j;
+            *reinterpret_cast<uint32_t *>(dst) = hi4;
+            *reinterpret_cast<uint32_t *>(dst + p.ld_out) = lo4;
+          }
+        } else {
+          if (tok_ok && nc < p.R) {
+            float4 *dst = reinterpret_cast<float4 *>(p.y_out + static_cast<size_t>(w.row0 + tok) * p.ld_out + nc);
+            dst[0] = make_float4(tot[0] + b[0], tot[1] + b[1], tot[2] + b[2], tot[3] + b[3]);
+            dst[1] = make_float4(tot[4] + b[4], tot[5] + b[5], tot[6] + b[6], tot[7] + b[7]);
           }
         }
       }

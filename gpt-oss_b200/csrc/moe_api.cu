@@ -3,6 +3,7 @@
 // reference runtime does around its MoE kernels (getp-csrc/getp_run.cpp:
 // malloc_gpu_run_state*, copy_weights_to_gpu_*, moe_gpu / moe_gpu_120b), minus
 // the host synchronisations: nothing in moe_forward() waits for the device.
+#include <cmath>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -52,30 +53,34 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// Packed weight codes viewed as bytes: [E][R][K/2], box = 64 bytes x 256 rows x 1.
-int make_weight_map(moe_ctx *c, CUtensorMap *m, const uint8_t *base, int E, int R, int K) {
+// Packed e2m1 weight codes [E][R][pitch bytes], declared to TMA as 4-bit elements that it expands to
+// the 8-bit containers of the block-scaled MMA (16U4_ALIGN16B).  That type wants the inner extent to be
+// a multiple of 128 elements, so it is rounded up: the last box of a row then reads a few bytes of the
+// next row (or of the slack behind the buffer), which meet zero-filled activations and scale 1.
+int make_weight_map(moe_ctx *c, CUtensorMap *m, const uint8_t *base, int E, int R, int K, int pitch) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(c, MOE_ERR_CUDA, "cuTensorMapEncodeTiled not available");
-  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(K / 2), static_cast<cuuint64_t>(R), static_cast<cuuint64_t>(E)};
-  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(K / 2), static_cast<cuuint64_t>(R) * (K / 2)};
-  const cuuint32_t box[3] = {kChunkK / 2, kPairRows, 1};
+  const cuuint64_t kvirt = static_cast<cuuint64_t>((K + 127) / 128) * 128;
+  const cuuint64_t dims[3] = {kvirt, static_cast<cuuint64_t>(R), static_cast<cuuint64_t>(E)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(pitch), static_cast<cuuint64_t>(R) * pitch};
+  const cuuint32_t box[3] = {kChunkK, kTileN, 1};
   const cuuint32_t es[3] = {1, 1, 1};
-  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t *>(base), dims, strides, box, es,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3, const_cast<uint8_t *>(base), dims, strides, box, es,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(c, MOE_ERR_CUDA, "cuTensorMapEncodeTiled(weights E=%d R=%d K=%d) -> %d", E, R, K, (int)r);
   return MOE_OK;
 }
 
-// fp16 activations [rows][K], box = 64 elements x 32 rows, 128-byte swizzle.
-int make_act_map(moe_ctx *c, CUtensorMap *m, const __half *base, int rows, int K) {
+// e4m3 activation rows [rows][K] (one byte each), box = 128 elements x 128 rows, 128-byte swizzle.
+int make_act_map(moe_ctx *c, CUtensorMap *m, const uint8_t *base, int rows, int K) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(c, MOE_ERR_CUDA, "cuTensorMapEncodeTiled not available");
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * 2};
-  const cuuint32_t box[2] = {kSubK, kXBoxRows};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K)};
+  const cuuint32_t box[2] = {kChunkK, kTileM};
   const cuuint32_t es[2] = {1, 1};
-  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half *>(base), dims, strides, box, es,
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(base), dims, strides, box, es,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(c, MOE_ERR_CUDA, "cuTensorMapEncodeTiled(activations rows=%d K=%d) -> %d", rows, K, (int)r);
@@ -101,17 +106,21 @@ int dev_alloc(moe_ctx *c, T **p, size_t n) {
   return MOE_OK;
 }
 
-// E8M0 scales of one weight matrix -> [E][n_pairs][n_kchunks][256 rows][4], 127 where no block exists.
-void tile_scales(const uint8_t *raw /*[E][R][nblk]*/, int E, int R, int nblk, int n_pairs, int n_kc,
+// E8M0 scales of one weight matrix -> [E][n_ntiles][n_kchunks][2 atoms][512]: the scales of a
+// work item's 240 weight rows for one 128-wide slice of k, in the order tcgen05.cp puts them into
+// tensor memory (row r of a 128-row atom, k block kb -> byte (r%32)*16 + (r/32)*4 + kb); 127
+// (scale 1) where no row or no block exists.
+void tile_scales(const uint8_t *raw /*[E][R][nblk]*/, int E, int R, int nblk, int n_ntiles, int n_kc,
                  std::vector<uint8_t> &out) {
-  out.assign(static_cast<size_t>(E) * n_pairs * n_kc * kScaleChunkBytes, 127);
+  out.assign(static_cast<size_t>(E) * n_ntiles * n_kc * kSfbChunkBytes, 127);
   for (int e = 0; e < E; ++e)
     for (int r = 0; r < R; ++r) {
       const uint8_t *src = raw + (static_cast<size_t>(e) * R + r) * nblk;
-      const int pair = r / kPairRows, rb = r % kPairRows;
+      const int nt = r / kTileN, rr = r % kTileN, atom = rr / 128, ra = rr % 128;
       for (int b = 0; b < nblk; ++b) {
-        const int kc = b / 4, c = b % 4;
-        out[((static_cast<size_t>(e) * n_pairs + pair) * n_kc + kc) * kScaleChunkBytes + rb * 4 + c] = src[b];
+        const int kc = b / 4, kb = b % 4;
+        out[((static_cast<size_t>(e) * n_ntiles + nt) * n_kc + kc) * kSfbChunkBytes + atom * kSfAtomBytes +
+            (ra % 32) * 16 + (ra / 32) * 4 + kb] = src[b];
       }
     }
 }
@@ -135,7 +144,7 @@ const char *moe_strerror(int code) {
     case MOE_ERR_CUDA: return "CUDA error";
     case MOE_ERR_NOMEM: return "out of memory";
     case MOE_ERR_TIMEOUT: return "a bounded wait ran out";
-    case MOE_ERR_SCALE_RANGE: return "E8M0 scale outside the fp16-exact range";
+    case MOE_ERR_SCALE_RANGE: return "E8M0 scale byte is NaN";
     case MOE_ERR_STATE: return "wrong state";
     case MOE_ERR_NO_SM100: return "device is not sm_100";
     default: return "unknown";
@@ -199,21 +208,43 @@ int moe_create(const moe_config *cfg, moe_handle *out) {
   if ((rc = dev_alloc(c, &c->ybuf, P * c->H))) return rc;
   if ((rc = dev_alloc(c, &c->out_f32, T * c->H))) return rc;
   if ((rc = dev_alloc(c, &c->out_bf16, T * c->H))) return rc;
-  const int n_pairs1 = (c->R1 + kPairRows - 1) / kPairRows, n_pairs2 = (c->H + kPairRows - 1) / kPairRows;
-  const int max_tiles = c->max_pairs / kTokTile + c->E + 1;
-  c->max_work1 = max_tiles * n_pairs1;
-  c->max_work2 = max_tiles * n_pairs2;
+  const int n_nt1 = (c->R1 + kTileN - 1) / kTileN, n_nt2 = (c->H + kTileN - 1) / kTileN;
+  c->max_tiles = c->max_pairs / kTokTile + c->E + 1;
+  c->max_work1 = c->max_tiles * n_nt1;
+  c->max_work2 = c->max_tiles * n_nt2;
+  // SwiGLU outputs are bounded by limit*(limit+1); they are stored as e4m3(h * 2^-h_exp) with the
+  // largest magnitude kept below 256 (e4m3 saturates at 448)
+  {
+    const float bound = fmaxf(c->cfg.swiglu_limit * (c->cfg.swiglu_limit + 1.0f), 1.0f);
+    c->h_exp = static_cast<int>(ceilf(log2f(bound))) - 8;
+  }
+  const size_t tile_rows = static_cast<size_t>(c->max_tiles) * kTileM;
+  if ((rc = dev_alloc(c, &c->xq, tile_rows * c->H))) return rc;
+  if ((rc = dev_alloc(c, &c->hq, tile_rows * c->Dl))) return rc;
+  if ((rc = dev_alloc(c, &c->sfa_x, static_cast<size_t>(c->max_tiles) * kSfAtomBytes))) return rc;
+  if ((rc = dev_alloc(c, &c->sfa_h, static_cast<size_t>(kSfAtomBytes)))) return rc;
+  if ((rc = dev_alloc(c, &c->tile_base, static_cast<size_t>(c->E) + 1))) return rc;
+  CU_TRY(c, cudaMemset(c->xq, 0, tile_rows * c->H));
+  CU_TRY(c, cudaMemset(c->hq, 0, tile_rows * c->Dl));
+  CU_TRY(c, cudaMemset(c->sfa_x, 127, static_cast<size_t>(c->max_tiles) * kSfAtomBytes));
+  {
+    uint8_t atom[kSfAtomBytes];
+    for (int r = 0; r < kTileM; ++r)
+      for (int kb = 0; kb < 4; ++kb)
+        atom[(r % 32) * 16 + (r / 32) * 4 + kb] = static_cast<uint8_t>(127 + c->h_exp - ((r & 1) ? 4 : 0));
+    CU_TRY(c, cudaMemcpy(c->sfa_h, atom, kSfAtomBytes, cudaMemcpyHostToDevice));
+  }
   if ((rc = dev_alloc(c, &c->work1, (size_t)c->max_work1))) return rc;
   if ((rc = dev_alloc(c, &c->work2, (size_t)c->max_work2))) return rc;
   if ((rc = dev_alloc(c, &c->n_work, (size_t)2))) return rc;
-  if ((rc = dev_alloc(c, &c->status, (size_t)1))) return rc;
-  CU_TRY(c, cudaMemset(c->status, 0, sizeof(unsigned)));
+  if ((rc = dev_alloc(c, &c->status, (size_t)4096))) return rc;
+  CU_TRY(c, cudaMemset(c->status, 0, 4096 * sizeof(unsigned)));
   CU_TRY(c, cudaMemset(c->n_work, 0, 2 * sizeof(int)));
   // Rows past the current batch are read (and discarded) by token tiles that overhang; keep them finite.
   CU_TRY(c, cudaMemset(c->xperm, 0, P * c->H * sizeof(__half)));
   CU_TRY(c, cudaMemset(c->hbuf, 0, P * c->Dl * sizeof(__half)));
-  if ((rc = make_act_map(c, &c->tm_x1, c->xperm, c->max_pairs, c->H))) return rc;
-  if ((rc = make_act_map(c, &c->tm_x2, c->hbuf, c->max_pairs, c->Dl))) return rc;
+  if ((rc = make_act_map(c, &c->tm_x1, c->xq, static_cast<int>(tile_rows), c->H))) return rc;
+  if ((rc = make_act_map(c, &c->tm_x2, c->hq, static_cast<int>(tile_rows), c->Dl))) return rc;
   return MOE_OK;
 }
 
@@ -222,10 +253,13 @@ int moe_destroy(moe_handle c) {
   cudaSetDevice(c->cfg.device);
   if (c->stream) { cudaStreamSynchronize(c->stream); cudaStreamDestroy(c->stream); }
   for (auto &w : c->layers) free_layer(w);
+  for (cudaEvent_t e : c->prof_events) cudaEventDestroy(e);
+  for (cudaEvent_t e : c->prof_pool) cudaEventDestroy(e);
   cudaFree(c->t_in); cudaFree(c->logits); cudaFree(c->topk_idx); cudaFree(c->topk_w); cudaFree(c->counts);
   cudaFree(c->offsets); cudaFree(c->pair_row); cudaFree(c->row_token); cudaFree(c->xperm); cudaFree(c->hbuf);
   cudaFree(c->ybuf); cudaFree(c->out_f32); cudaFree(c->out_bf16); cudaFree(c->work1); cudaFree(c->work2);
   cudaFree(c->n_work); cudaFree(c->status);
+  cudaFree(c->xq); cudaFree(c->hq); cudaFree(c->sfa_x); cudaFree(c->sfa_h); cudaFree(c->tile_base);
   delete c;
   return MOE_OK;
 }
@@ -244,34 +278,36 @@ int moe_load_layer(moe_handle c, int layer, const uint8_t *w1_codes, const uint8
   // ---- this rank's shard, still in the reference layout -------------------
   // MLP1: rows [2*d0, 2*(d0+Dl)) of every expert (gate/up pairs stay adjacent);
   // MLP2: columns [d0, d0+Dl).  Scale blocks (32 along the input dim) are never cut.
-  const size_t w1_row = H / 2, s1_row = H / 32;
-  std::vector<uint8_t> c1(static_cast<size_t>(E) * R1 * w1_row), s1(static_cast<size_t>(E) * R1 * s1_row);
+  // Row pitch of the packed codes: K/2 bytes rounded up to 32 (a TMA requirement of the 4-bit
+  // element type); pad bytes are zero codes.
+  const size_t w1_row = H / 2, s1_row = H / 32, p1 = (w1_row + 31) / 32 * 32;
+  std::vector<uint8_t> c1(static_cast<size_t>(E) * R1 * p1, 0), s1(static_cast<size_t>(E) * R1 * s1_row);
   std::vector<uint16_t> bb1(static_cast<size_t>(E) * R1);
   for (int e = 0; e < E; ++e) {
     const size_t src_row0 = static_cast<size_t>(e) * 2 * D + 2 * d0;
-    memcpy(&c1[static_cast<size_t>(e) * R1 * w1_row], w1_codes + src_row0 * w1_row, static_cast<size_t>(R1) * w1_row);
+    for (int r = 0; r < R1; ++r)
+      memcpy(&c1[(static_cast<size_t>(e) * R1 + r) * p1], w1_codes + (src_row0 + r) * w1_row, w1_row);
     memcpy(&s1[static_cast<size_t>(e) * R1 * s1_row], w1_scales + src_row0 * s1_row, static_cast<size_t>(R1) * s1_row);
     memcpy(&bb1[static_cast<size_t>(e) * R1], b1 + src_row0, static_cast<size_t>(R1) * 2);
   }
-  const size_t w2_row = Dl / 2, s2_row = Dl / 32;
-  std::vector<uint8_t> c2(static_cast<size_t>(E) * H * w2_row), s2(static_cast<size_t>(E) * H * s2_row);
+  const size_t w2_row = Dl / 2, s2_row = Dl / 32, p2 = (w2_row + 31) / 32 * 32;
+  std::vector<uint8_t> c2(static_cast<size_t>(E) * H * p2, 0), s2(static_cast<size_t>(E) * H * s2_row);
   for (size_t r = 0; r < static_cast<size_t>(E) * H; ++r) {
-    memcpy(&c2[r * w2_row], w2_codes + r * (D / 2) + d0 / 2, w2_row);
+    memcpy(&c2[r * p2], w2_codes + r * (D / 2) + d0 / 2, w2_row);
     memcpy(&s2[r * s2_row], w2_scales + r * (D / 32) + d0 / 32, s2_row);
   }
-  // every scaled code must be an exact fp16 value: exponent in [-23, 13]
+  c->pitch1 = static_cast<int>(p1);
+  c->pitch2 = static_cast<int>(p2);
+  // 0xFF is the NaN encoding of E8M0; every other byte is a valid power of two for the tensor core
   for (const std::vector<uint8_t> *sv : {&s1, &s2})
-    for (uint8_t b : *sv) {
-      const int e8 = static_cast<int>(b) - 127;
-      if (e8 < -23 || e8 > 13)
-        return fail(c, MOE_ERR_SCALE_RANGE, "layer %d: E8M0 exponent %d outside [-23, 13]", layer, e8);
-    }
+    for (uint8_t b : *sv)
+      if (b == 0xFF) return fail(c, MOE_ERR_SCALE_RANGE, "layer %d: E8M0 scale byte 0xFF (NaN)", layer);
 
-  const int n_pairs1 = (R1 + kPairRows - 1) / kPairRows, n_kc1 = (H + kChunkK - 1) / kChunkK;
-  const int n_pairs2 = (H + kPairRows - 1) / kPairRows, n_kc2 = (Dl + kChunkK - 1) / kChunkK;
+  const int n_nt1 = (R1 + kTileN - 1) / kTileN, n_kc1 = (H + kChunkK - 1) / kChunkK;
+  const int n_nt2 = (H + kTileN - 1) / kTileN, n_kc2 = (Dl + kChunkK - 1) / kChunkK;
   std::vector<uint8_t> t1, t2;
-  tile_scales(s1.data(), E, R1, H / 32, n_pairs1, n_kc1, t1);
-  tile_scales(s2.data(), E, H, Dl / 32, n_pairs2, n_kc2, t2);
+  tile_scales(s1.data(), E, R1, H / 32, n_nt1, n_kc1, t1);
+  tile_scales(s2.data(), E, H, Dl / 32, n_nt2, n_kc2, t2);
 
   // router weight as three bf16 planes whose sum is the fp32 value exactly
   std::vector<uint16_t> w3(static_cast<size_t>(3) * E * H);
@@ -308,8 +344,8 @@ int moe_load_layer(moe_handle c, int layer, const uint8_t *w1_codes, const uint8
   CU_TRY(c, cudaMemcpy(w.b2, b2, static_cast<size_t>(E) * H * 2, cudaMemcpyHostToDevice));
   CU_TRY(c, cudaMemcpy(w.router_w3, w3.data(), w3.size() * 2, cudaMemcpyHostToDevice));
   CU_TRY(c, cudaMemcpy(w.router_b, router_b, static_cast<size_t>(E) * 4, cudaMemcpyHostToDevice));
-  if ((rc = make_weight_map(c, &w.tm_w1, w.w1_codes, E, R1, H))) return rc;
-  if ((rc = make_weight_map(c, &w.tm_w2, w.w2_codes, E, H, Dl))) return rc;
+  if ((rc = make_weight_map(c, &w.tm_w1, w.w1_codes, E, R1, H, c->pitch1))) return rc;
+  if ((rc = make_weight_map(c, &w.tm_w2, w.w2_codes, E, H, Dl, c->pitch2))) return rc;
   w.loaded = true;
   return MOE_OK;
 }
@@ -334,38 +370,57 @@ int moe_forward(moe_handle c, int layer, const void *t_dev, int rows, void *out_
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int T = rows, P = rows * c->K, E = c->E, H = c->H, K = c->K;
   const __nv_bfloat16 *t = static_cast<const __nv_bfloat16 *>(t_dev);
-  const int n_pairs1 = (c->R1 + kPairRows - 1) / kPairRows, n_pairs2 = (H + kPairRows - 1) / kPairRows;
+  const int n_nt1 = (c->R1 + kTileN - 1) / kTileN, n_nt2 = (H + kTileN - 1) / kTileN;
 
   CU_TRY(c, cudaMemsetAsync(c->counts, 0, sizeof(int) * E, s));
+  auto mark = [&]() {
+    if (!c->profiling) return;
+    cudaEvent_t ev;
+    if (!c->prof_pool.empty()) { ev = c->prof_pool.back(); c->prof_pool.pop_back(); }
+    else if (cudaEventCreate(&ev) != cudaSuccess) return;
+    cudaEventRecord(ev, s);
+    c->prof_events.push_back(ev);
+  };
+  mark();
   launch_router_logits(t, w.router_w3, w.router_b, c->logits, T, H, E, s);
+  mark();
   launch_topk_softmax(c->logits, T, E, K, c->topk_idx, c->topk_w, c->counts, s);
-  launch_build_index(c->topk_idx, c->counts, T, E, K, n_pairs1, n_pairs2, c->offsets, c->pair_row, c->row_token,
-                     c->work1, c->work2, c->n_work, c->max_work1, c->max_work2, c->status, s);
-  launch_gather_rows(t, c->row_token, c->offsets, E, c->xperm, H, P, s);
+  mark();
+  launch_build_index(c->topk_idx, c->counts, T, E, K, n_nt1, n_nt2, c->offsets, c->tile_base, c->pair_row,
+                     c->row_token, c->work1, c->work2, c->n_work, c->max_work1, c->max_work2, c->status, s);
+  mark();
+  if (flags & MOE_FWD_SIMT_GEMM) launch_gather_rows(t, c->row_token, c->offsets, E, c->xperm, H, P, s);
+  else launch_quantize_rows(t, c->row_token, c->offsets, c->tile_base, E, c->xq, c->sfa_x, H, P, s);
+  mark();
   const int add_b2 = c->cfg.tp_rank == 0 ? 1 : 0;
   if (flags & MOE_FWD_SIMT_GEMM) {
-    launch_simt_mlp1(w.w1_codes, w.w1_scales_raw, w.b1, c->xperm, c->offsets, E, H, c->R1, c->hbuf,
+    launch_simt_mlp1(w.w1_codes, c->pitch1, w.w1_scales_raw, w.b1, c->xperm, c->offsets, E, H, c->R1, c->hbuf,
                      c->cfg.swiglu_limit, c->cfg.swiglu_alpha, P, s);
-    launch_simt_mlp2(w.w2_codes, w.w2_scales_raw, w.b2, add_b2, c->hbuf, c->offsets, E, c->Dl, H, c->ybuf, P, s);
+    mark();
+    launch_simt_mlp2(w.w2_codes, c->pitch2, w.w2_scales_raw, w.b2, add_b2, c->hbuf, c->offsets, E, c->Dl, H,
+                     c->ybuf, P, s);
   } else {
     GemmArgs a{};
     a.work = c->work1; a.n_work = c->n_work; a.K = H; a.R = c->R1;
-    a.n_kchunks = (H + kChunkK - 1) / kChunkK; a.n_pairs = n_pairs1;
-    a.scales = w.w1_scales; a.bias = w.b1; a.add_bias = 1;
-    a.h_out = c->hbuf; a.y_out = nullptr; a.ld_out = c->Dl;
+    a.n_kchunks = (H + kChunkK - 1) / kChunkK; a.n_ntiles = n_nt1;
+    a.sfb = w.w1_scales; a.sfa = c->sfa_x; a.sfa_tile_stride = kSfAtomBytes; a.bias = w.b1; a.add_bias = 1;
+    a.hq_out = c->hq; a.y_out = nullptr; a.ld_out = c->Dl; a.h_exp = c->h_exp;
     a.limit = c->cfg.swiglu_limit; a.alpha = c->cfg.swiglu_alpha; a.status = c->status;
     launch_expert_gemm_mlp1(w.tm_w1, c->tm_x1, a, c->sm_count, s);
+    mark();
     GemmArgs b = a;
     b.work = c->work2; b.n_work = c->n_work + 1; b.K = c->Dl; b.R = H;
-    b.n_kchunks = (c->Dl + kChunkK - 1) / kChunkK; b.n_pairs = n_pairs2;
-    b.scales = w.w2_scales; b.bias = w.b2; b.add_bias = add_b2;
-    b.h_out = nullptr; b.y_out = c->ybuf; b.ld_out = H;
+    b.n_kchunks = (c->Dl + kChunkK - 1) / kChunkK; b.n_ntiles = n_nt2;
+    b.sfb = w.w2_scales; b.sfa = c->sfa_h; b.sfa_tile_stride = 0; b.bias = w.b2; b.add_bias = add_b2;
+    b.hq_out = nullptr; b.y_out = c->ybuf; b.ld_out = H;
     launch_expert_gemm_mlp2(w.tm_w2, c->tm_x2, b, c->sm_count, s);
   }
+  mark();
   const bool partial = (flags & MOE_FWD_PARTIAL_F32) != 0;
   const bool keep_f32 = partial || (c->cfg.flags & MOE_CFG_KEEP_F32_OUT);
   launch_combine(c->ybuf, c->topk_idx, c->topk_w, c->pair_row, T, H, K,
                  partial ? nullptr : static_cast<__nv_bfloat16 *>(out_dev), keep_f32 ? c->out_f32 : nullptr, s);
+  mark();
   c->launches += 7;
   c->last_rows = rows;
   CU_TRY(c, cudaGetLastError());
@@ -404,6 +459,32 @@ int moe_forward_host(moe_handle c, int layer, const void *t_host, int rows, void
   return MOE_OK;
 }
 
+int moe_profile_enable(moe_handle c, int on) {
+  if (!c) return MOE_ERR_INVALID;
+  c->profiling = on != 0;
+  return MOE_OK;
+}
+
+int moe_profile_collect(moe_handle c, float *ms, int *n_calls) {
+  if (!c || !ms || !n_calls) return MOE_ERR_INVALID;
+  CU_TRY(c, cudaSetDevice(c->cfg.device));
+  const size_t per = MOE_N_STAGES + 1;
+  const size_t calls = c->prof_events.size() / per;
+  for (int i = 0; i < MOE_N_STAGES; ++i) ms[i] = 0.f;
+  for (size_t k = 0; k < calls; ++k) {
+    CU_TRY(c, cudaEventSynchronize(c->prof_events[k * per + MOE_N_STAGES]));
+    for (int i = 0; i < MOE_N_STAGES; ++i) {
+      float t = 0.f;
+      CU_TRY(c, cudaEventElapsedTime(&t, c->prof_events[k * per + i], c->prof_events[k * per + i + 1]));
+      ms[i] += t;
+    }
+  }
+  for (cudaEvent_t e : c->prof_events) c->prof_pool.push_back(e);
+  c->prof_events.clear();
+  *n_calls = static_cast<int>(calls);
+  return MOE_OK;
+}
+
 void *moe_host_alloc(size_t bytes) {
   void *p = nullptr;
   if (cudaHostAlloc(&p, bytes, cudaHostAllocDefault) != cudaSuccess) return nullptr;
@@ -428,8 +509,7 @@ int moe_get_debug(moe_handle c, int which, void *dst, size_t bytes) {
     case MOE_DBG_PAIR_ROW: src = c->pair_row; have = T * c->K * 4; break;
     case MOE_DBG_ROW_TOKEN: src = c->row_token; have = T * c->K * 4; break;
     case MOE_DBG_OUT_F32: src = c->out_f32; have = T * c->H * 4; break;
-    case MOE_DBG_STATUS: src = c->status; have = 4; break;
-    case MOE_DBG_HBUF: src = c->hbuf; have = T * c->K * c->Dl * 2; break;
+    case MOE_DBG_STATUS: src = c->status; have = 4096 * 4; break;
     case MOE_DBG_YBUF: src = c->ybuf; have = T * c->K * c->H * 4; break;
     default: return fail(c, MOE_ERR_INVALID, "moe_get_debug: unknown item %d", which);
   }

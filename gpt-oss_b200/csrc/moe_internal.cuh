@@ -14,13 +14,13 @@
 namespace moe {
 
 // ---- tiling constants of the expert GEMM (expert_gemm_sm100.cu) -------------
-constexpr int kTileRows = 128;    // weight rows per MMA tile (UMMA M)
-constexpr int kPairRows = 256;    // weight rows per work item (two MMA tiles share one token tile)
-constexpr int kChunkK = 128;      // reduction elements per shared-memory stage
-constexpr int kSubK = 64;         // reduction elements per tensor-memory A buffer
-constexpr int kTokTile = 96;      // most token rows per work item (UMMA N <= 96)
-constexpr int kXBoxRows = 32;     // token rows per TMA box
-constexpr int kScaleChunkBytes = kPairRows * (kChunkK / 32);  // 1024: scales of one stage
+constexpr int kTileN = 240;        // weight rows per work item (UMMA N); divides 5760 and 2880
+constexpr int kTileNPad = 256;     // rows reserved per weight tile in shared memory / scale atoms
+constexpr int kChunkK = 128;       // reduction elements per shared-memory stage (4 MMA k-steps of 32)
+constexpr int kTokTile = 64;       // token rows per work item
+constexpr int kTileM = 2 * kTokTile;  // UMMA M: each token contributes a high and a low e4m3 row
+constexpr int kSfAtomBytes = 512;  // scale factors of 128 rows x 4 k-blocks, tensor-memory order
+constexpr int kSfbChunkBytes = 2 * kSfAtomBytes;  // weight scales of one stage (256 rows)
 
 // Device status bits (MOE_DBG_STATUS).
 enum : unsigned {
@@ -37,9 +37,11 @@ enum : unsigned {
 // One work item of the grouped GEMM.
 struct __align__(16) WorkItem {
   int expert;  // expert index
-  int pair;    // 256-row block of that expert's weight matrix
+  int ntile;   // kTileN-row block of that expert's weight matrix
+  int tile;    // global token-tile index (rows tile*kTileM .. of the quantised activations)
   int row0;    // first permuted row of the token tile
   int ntok;    // valid token rows in the tile (1..kTokTile)
+  int pad[3];
 };
 
 struct GemmArgs {
@@ -48,21 +50,24 @@ struct GemmArgs {
   int K;          // reduction length in elements (multiple of 32)
   int R;          // weight rows per expert on this rank
   int n_kchunks;  // ceil(K / kChunkK)
-  int n_pairs;    // ceil(R / kPairRows)
-  const uint8_t *scales;      // [E][n_pairs][n_kchunks][256][4] E8M0, padded with 127
+  int n_ntiles;   // ceil(R / kTileN)
+  const uint8_t *sfb;         // weight scales [E][n_ntiles][n_kchunks][2 atoms][512], 127 where no block exists
+  const uint8_t *sfa;         // activation scales, one 512-byte atom per token tile
+  int sfa_tile_stride;        // bytes between token tiles' atoms (0: one atom shared by all tiles)
   const __nv_bfloat16 *bias;  // [E][R]
   int add_bias;               // MLP2 on TP ranks other than 0 leaves the bias out
-  __half *h_out;              // MLP1: [P, ld_out] fp16 SwiGLU output
+  uint8_t *hq_out;            // MLP1: quantised SwiGLU output [tiles*kTileM, ld_out] e4m3 (high/low rows)
   float *y_out;               // MLP2: [P, ld_out] fp32
   int ld_out;
+  int h_exp;                  // MLP1: SwiGLU outputs are stored as e4m3(h * 2^-h_exp)
   float limit, alpha;
   unsigned int *status;
 };
 
 struct LayerWeights {
   bool loaded = false;
-  uint8_t *w1_codes = nullptr;   // [E, R1, H/2]
-  uint8_t *w1_scales = nullptr;  // repacked, see GemmArgs::scales
+  uint8_t *w1_codes = nullptr;   // [E, R1, pitch1] packed e2m1, pitch = K/2 rounded up to 32 bytes
+  uint8_t *w1_scales = nullptr;  // repacked, see GemmArgs::sfb
   __nv_bfloat16 *b1 = nullptr;   // [E, R1]
   uint8_t *w2_codes = nullptr;   // [E, H, Dl/2]
   uint8_t *w2_scales = nullptr;
@@ -96,8 +101,16 @@ struct moe_ctx {
   int *offsets = nullptr;           // d_expert_offsets    [E+1]
   int *pair_row = nullptr;          // local_ids_g         [max_rows, K]
   int *row_token = nullptr;         // expert_row_token_g  [max_pairs]
-  __half *xperm = nullptr;          // expert_input_buffer [max_pairs, H]   fp16
-  __half *hbuf = nullptr;           // gate_up             [max_pairs, Dl]  fp16
+  __half *xperm = nullptr;          // expert_input_buffer [max_pairs, H]   fp16 (validation GEMM only)
+  __half *hbuf = nullptr;           // gate_up             [max_pairs, Dl]  fp16 (validation GEMM only)
+  uint8_t *xq = nullptr;            // expert_input_buffer as e4m3 high/low rows [max_tiles*128, H]
+  uint8_t *hq = nullptr;            // gate_up as e4m3 high/low rows            [max_tiles*128, Dl]
+  uint8_t *sfa_x = nullptr;         // per-tile scale atoms of xq [max_tiles][512]
+  uint8_t *sfa_h = nullptr;         // the one scale atom of hq   [512]
+  int *tile_base = nullptr;         // first token tile of each expert [E+1]
+  int max_tiles = 0;
+  int h_exp = 0;                    // hq holds e4m3(h * 2^-h_exp)
+  int pitch1 = 0, pitch2 = 0;       // bytes per packed weight row (MLP1, MLP2)
   float *ybuf = nullptr;            // expert_output_partial [max_pairs, H] fp32
   float *out_f32 = nullptr;         // fp32 block output   [max_rows, H] (debug / TP partial)
   __nv_bfloat16 *out_bf16 = nullptr;// e_agg_g             [max_rows, H]
@@ -108,6 +121,9 @@ struct moe_ctx {
   CUtensorMap tm_x1, tm_x2;
   int last_rows = 0;
   long long launches = 0;
+  bool profiling = false;
+  std::vector<cudaEvent_t> prof_events;  // MOE_N_STAGES + 1 per profiled call
+  std::vector<cudaEvent_t> prof_pool;    // recycled events
   std::string err;
 };
 
@@ -118,9 +134,12 @@ void launch_router_logits(const __nv_bfloat16 *t, const __nv_bfloat16 *w3, const
                           int T, int H, int E, cudaStream_t s);
 void launch_topk_softmax(const float *logits, int T, int E, int K, int *idx, float *w, int *counts,
                          cudaStream_t s);
-void launch_build_index(const int *topk_idx, const int *counts, int T, int E, int K, int n_pairs1, int n_pairs2,
-                        int *offsets, int *pair_row, int *row_token, WorkItem *work1, WorkItem *work2,
-                        int *n_work, int max_work1, int max_work2, unsigned int *status, cudaStream_t s);
+void launch_build_index(const int *topk_idx, const int *counts, int T, int E, int K, int n_ntiles1, int n_ntiles2,
+                        int *offsets, int *tile_base, int *pair_row, int *row_token, WorkItem *work1,
+                        WorkItem *work2, int *n_work, int max_work1, int max_work2, unsigned int *status,
+                        cudaStream_t s);
+void launch_quantize_rows(const __nv_bfloat16 *t, const int *row_token, const int *offsets, const int *tile_base,
+                          int E, uint8_t *xq, uint8_t *sfa, int H, int n_rows, cudaStream_t s);
 void launch_gather_rows(const __nv_bfloat16 *t, const int *row_token, const int *offsets, int E, __half *xperm,
                         int H, int max_pairs, cudaStream_t s);
 void launch_combine(const float *y, const int *topk_idx, const float *topk_w, const int *pair_row, int T, int H,
@@ -134,11 +153,11 @@ void launch_expert_gemm_mlp2(const CUtensorMap &tm_w, const CUtensorMap &tm_x, c
                              cudaStream_t s);
 
 // expert_gemm_simt.cu (validation path)
-void launch_simt_mlp1(const uint8_t *codes, const uint8_t *scales_raw, const __nv_bfloat16 *bias, const __half *x,
-                      const int *offsets, int E, int H, int R1, __half *h_out, float limit, float alpha,
+void launch_simt_mlp1(const uint8_t *codes, int pitch, const uint8_t *scales_raw, const __nv_bfloat16 *bias,
+                      const __half *x, const int *offsets, int E, int H, int R1, __half *h_out, float limit,
+                      float alpha, int n_rows, cudaStream_t s);
+void launch_simt_mlp2(const uint8_t *codes, int pitch, const uint8_t *scales_raw, const __nv_bfloat16 *bias,
+                      int add_bias, const __half *h, const int *offsets, int E, int Dl, int H, float *y_out,
                       int n_rows, cudaStream_t s);
-void launch_simt_mlp2(const uint8_t *codes, const uint8_t *scales_raw, const __nv_bfloat16 *bias, int add_bias,
-                      const __half *h, const int *offsets, int E, int Dl, int H, float *y_out, int n_rows,
-                      cudaStream_t s);
 
 }  // namespace moe

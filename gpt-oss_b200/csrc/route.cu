@@ -4,6 +4,8 @@
 // reference's per-layer host round trip (expert counts copied to the host, tile
 // maps built there, getp-csrc/getp_run.cpp:2648-2692 and :3019-3068) is replaced
 // by build_index_kernel.
+#include <cuda_fp8.h>
+
 #include "moe_internal.cuh"
 
 namespace moe {
@@ -174,9 +176,10 @@ void launch_topk_softmax(const float *logits, int T, int E, int K, int *idx, flo
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ counts, int T, int E, int K,
-                   int n_pairs1, int n_pairs2, int *__restrict__ offsets, int *__restrict__ pair_row,
-                   int *__restrict__ row_token, WorkItem *__restrict__ work1, WorkItem *__restrict__ work2,
-                   int *__restrict__ n_work, int max_work1, int max_work2, unsigned int *status) {
+                   int n_ntiles1, int n_ntiles2, int *__restrict__ offsets, int *__restrict__ tile_base,
+                   int *__restrict__ pair_row, int *__restrict__ row_token, WorkItem *__restrict__ work1,
+                   WorkItem *__restrict__ work2, int *__restrict__ n_work, int max_work1, int max_work2,
+                   unsigned int *status) {
   __shared__ int s_red[2][8];
   __shared__ int s_warp[8];
   __shared__ int s_running;
@@ -201,9 +204,11 @@ build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ cou
 #pragma unroll
   for (int i = 0; i < 8; ++i) { off += s_red[0][i]; tiles_before += s_red[1][i]; }
   const int cnt = counts[e];
+  const int ntt = (cnt + kTokTile - 1) / kTokTile;  // token tiles of this expert (rows e's tiles, in order)
   if (tid == 0) {
     offsets[e] = off;
-    if (e == E - 1) offsets[E] = off + cnt;
+    tile_base[e] = tiles_before;
+    if (e == E - 1) { offsets[E] = off + cnt; tile_base[E] = tiles_before + ntt; }
   }
 
   // stable compaction in ascending token order
@@ -237,33 +242,126 @@ build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ cou
   }
   if (tid == 0 && s_running != cnt) atomicOr(status, ST_BAD_INDEX);
 
-  // work items: token tiles of at most kTokTile rows, evenly sized
-  const int ntt = (cnt + kTokTile - 1) / kTokTile;
-  const int ts = ntt ? (cnt + ntt - 1) / ntt : 0;
+  // work items: one per (token tile of kTokTile rows, block of kTileN weight rows); items that share a
+  // weight block are adjacent so that block is fetched from HBM once and re-read from L2
   for (int which = 0; which < 2; ++which) {
-    const int np = which ? n_pairs2 : n_pairs1;
+    const int nn = which ? n_ntiles2 : n_ntiles1;
     WorkItem *work = which ? work2 : work1;
     const int cap = which ? max_work2 : max_work1;
-    const int start = tiles_before * np;
-    for (int i = tid; i < ntt * np; i += blockDim.x) {
-      const int pair = i / ntt, tt = i % ntt;
+    const int start = tiles_before * nn;
+    for (int i = tid; i < ntt * nn; i += blockDim.x) {
+      const int ntile = i / ntt, tt = i % ntt;
       WorkItem it;
       it.expert = e;
-      it.pair = pair;
-      it.row0 = off + tt * ts;
-      it.ntok = min(ts, cnt - tt * ts);
+      it.ntile = ntile;
+      it.tile = tiles_before + tt;
+      it.row0 = off + tt * kTokTile;
+      it.ntok = min(kTokTile, cnt - tt * kTokTile);
+      it.pad[0] = it.pad[1] = it.pad[2] = 0;
       if (start + i < cap) work[start + i] = it;
       else atomicOr(status, ST_BAD_INDEX);
     }
-    if (e == E - 1 && tid == 0) n_work[which] = min((tiles_before + ntt) * np, cap);
+    if (e == E - 1 && tid == 0) n_work[which] = min((tiles_before + ntt) * nn, cap);
   }
 }
 
-void launch_build_index(const int *topk_idx, const int *counts, int T, int E, int K, int n_pairs1, int n_pairs2,
-                        int *offsets, int *pair_row, int *row_token, WorkItem *work1, WorkItem *work2,
-                        int *n_work, int max_work1, int max_work2, unsigned int *status, cudaStream_t s) {
-  build_index_kernel<<<E, 256, 0, s>>>(topk_idx, counts, T, E, K, n_pairs1, n_pairs2, offsets, pair_row,
-                                       row_token, work1, work2, n_work, max_work1, max_work2, status);
+void launch_build_index(const int *topk_idx, const int *counts, int T, int E, int K, int n_ntiles1, int n_ntiles2,
+                        int *offsets, int *tile_base, int *pair_row, int *row_token, WorkItem *work1,
+                        WorkItem *work2, int *n_work, int max_work1, int max_work2, unsigned int *status,
+                        cudaStream_t s) {
+  build_index_kernel<<<E, 256, 0, s>>>(topk_idx, counts, T, E, K, n_ntiles1, n_ntiles2, offsets, tile_base,
+                                       pair_row, row_token, work1, work2, n_work, max_work1, max_work2, status);
+}
+
+// ---------------------------------------------------------------------------
+// Row gather + quantisation for the tensor-core GEMM.  Reference:
+// pack_rows_kernel_bf16_in (kernels/moe.hpp:983-1048) copies bf16 rows; here
+// each gathered row becomes TWO e4m3 rows (the block-scaled MMA has no bf16
+// operand): with s = 2^e chosen so that the row's largest |x|/s lies in
+// [128, 256), high = e4m3(x/s) and low = e4m3((x/s - high) * 16).  A bf16 value
+// has 8 significant bits, the high term keeps 4 of them and the residual fits the
+// 4 of the low term, so high + low/16 == x/s exactly unless x is more than 2^13
+// below the row maximum.  Row 2i of a 128-row token tile is the high term of the
+// tile's token i, row 2i+1 the low term; their UE8M0 scales (127+e, 127+e-4) go
+// into the tile's 512-byte scale atom, byte (r%32)*16 + (r/32)*4 + kb for row r
+// and every k block kb (the scale is per row, so the four bytes are equal).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+quantize_rows_kernel(const __nv_bfloat16 *__restrict__ t, const int *__restrict__ row_token,
+                     const int *__restrict__ offsets, const int *__restrict__ tile_base, int E,
+                     uint8_t *__restrict__ xq, uint8_t *__restrict__ sfa, int H) {
+  __shared__ float s_max[4];
+  const int r = blockIdx.x;
+  if (r >= offsets[E]) return;
+  int lo = 0, hi = E;  // expert of this permuted row: offsets[lo] <= r < offsets[hi]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (offsets[mid] <= r) lo = mid; else hi = mid;
+  }
+  const int pos = r - offsets[lo];
+  const int tile = tile_base[lo] + pos / kTokTile, i = pos % kTokTile;
+  const int tok = row_token[r];
+  const uint4 *src = reinterpret_cast<const uint4 *>(t + static_cast<size_t>(tok) * H);
+  float amax = 0.f;
+  for (int c = threadIdx.x; c < H / 8; c += blockDim.x) {
+    const uint4 v = __ldg(src + c);
+    const uint32_t in[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      amax = fmaxf(amax, fabsf(__uint_as_float(in[j] << 16)));
+      amax = fmaxf(amax, fabsf(__uint_as_float(in[j] & 0xffff0000u)));
+    }
+  }
+#pragma unroll
+  for (int off = 16; off; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = fmaxf(fmaxf(s_max[0], s_max[1]), fmaxf(s_max[2], s_max[3]));
+  // e = floor(log2(amax)) - 7, kept where both scales stay valid UE8M0 bytes
+  int e = static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu) - 127 - 7;
+  e = max(-120, min(e, 120));
+  const float inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);  // 2^-e
+  uint8_t *row_hi = xq + (static_cast<size_t>(tile) * kTileM + 2 * i) * H;
+  uint8_t *row_lo = row_hi + H;
+  for (int c = threadIdx.x; c < H / 8; c += blockDim.x) {
+    const uint4 v = __ldg(src + c);
+    const uint32_t in[4] = {v.x, v.y, v.z, v.w};
+    float f[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      f[2 * j] = __uint_as_float(in[j] << 16) * inv;
+      f[2 * j + 1] = __uint_as_float(in[j] & 0xffff0000u) * inv;
+    }
+    uint32_t h8[2], l8[2];
+#pragma unroll
+    for (int g = 0; g < 2; ++g) {
+      const uint32_t a = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * g], f[4 * g + 1]), __NV_SATFINITE, __NV_E4M3);
+      const uint32_t b = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * g + 2], f[4 * g + 3]), __NV_SATFINITE, __NV_E4M3);
+      h8[g] = a | (b << 16);
+      float rs[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const __half_raw hr = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>((h8[g] >> (8 * j)) & 0xffu), __NV_E4M3);
+        rs[j] = (f[4 * g + j] - __half2float(*reinterpret_cast<const __half *>(&hr))) * 16.0f;
+      }
+      const uint32_t c2 = __nv_cvt_float2_to_fp8x2(make_float2(rs[0], rs[1]), __NV_SATFINITE, __NV_E4M3);
+      const uint32_t d2 = __nv_cvt_float2_to_fp8x2(make_float2(rs[2], rs[3]), __NV_SATFINITE, __NV_E4M3);
+      l8[g] = c2 | (d2 << 16);
+    }
+    reinterpret_cast<uint2 *>(row_hi)[c] = make_uint2(h8[0], h8[1]);
+    reinterpret_cast<uint2 *>(row_lo)[c] = make_uint2(l8[0], l8[1]);
+  }
+  if (threadIdx.x < 2) {
+    const int rr = 2 * i + threadIdx.x;  // row inside the tile: even = high, odd = low
+    const uint32_t byte = static_cast<uint32_t>(127 + e - 4 * static_cast<int>(threadIdx.x));
+    uint8_t *atom = sfa + static_cast<size_t>(tile) * kSfAtomBytes;
+    *reinterpret_cast<uint32_t *>(atom + (rr % 32) * 16 + (rr / 32) * 4) = byte * 0x01010101u;
+  }
+}
+
+void launch_quantize_rows(const __nv_bfloat16 *t, const int *row_token, const int *offsets, const int *tile_base,
+                          int E, uint8_t *xq, uint8_t *sfa, int H, int n_rows, cudaStream_t s) {
+  quantize_rows_kernel<<<n_rows, 128, 0, s>>>(t, row_token, offsets, tile_base, E, xq, sfa, H);
 }
 
 // ---------------------------------------------------------------------------

@@ -186,6 +186,47 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
   return d;
 }
 
+// D[tmem] (+)= (A * SFA) * (B * SFB)^T, kind::mxf8f6f4 with one UE8M0 scale per 32
+// elements of K for every row of A and of B; A and B from shared memory, scale
+// factors from tensor memory, M = 128, K = 32 per instruction.
+__device__ __forceinline__ void mma_mxf8f6f4_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate, uint32_t sfa_tmem, uint32_t sfb_tmem) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+
+// Instruction descriptor, kind::mxf8f6f4 block scaled: A = e4m3, B = e2m1 (4-bit
+// codes in 8-bit containers as the 16U4_ALIGN16B tensor map writes them), both
+// K-major, UE8M0 scales, M = 128, N = n.  sf_id selects which of the four scale
+// bytes of a tensor-memory column (which 32-wide k block of a 128-wide slice)
+// the instruction applies, for A and for B.
+__host__ __device__ constexpr uint32_t idesc_mxf8f6f4_m128(uint32_t n, uint32_t sf_id) {
+  return (sf_id << 4)          // B scale-factor id
+         | (0u << 7)           // A format = E4M3
+         | (5u << 10)          // B format = E2M1
+         | ((n >> 3) << 17)    // N >> 3
+         | (1u << 23)          // scale format = UE8M0
+         | ((128u >> 4) << 24) // M >> 4
+         | (sf_id << 29);      // A scale-factor id
+}
+
+// Copies one 512-byte scale-factor atom (32 rows x 16 bytes, no swizzle) from
+// shared memory into 4 tensor-memory columns, replicated into all four 32-lane
+// quadrants.  Byte (r % 32) * 16 + (r / 32) * 4 + kb of the atom is the scale of
+// row r, k block kb.  Issued by one thread; ordered before later tcgen05.mma of
+// the same thread.
+__device__ __forceinline__ void tmem_cp_sf_atom(uint32_t taddr, uint32_t saddr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);  // start address
+  d |= static_cast<uint64_t>(128 >> 4) << 32;           // stride between 8-row groups: 8 x 16 bytes
+  d |= static_cast<uint64_t>(1) << 46;                  // descriptor version of sm_100
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(d) : "memory");
+}
+
 // ---------------------------------------------------------------- MXFP4 decode
 // Four bytes = eight e2m1 codes (low nibble = even element) -> four packed
 // fp16 pairs, element order preserved (pair i = elements 2i, 2i+1).

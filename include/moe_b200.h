@@ -30,7 +30,7 @@ enum {
   MOE_ERR_CUDA = 2,        /* a CUDA call failed; see moe_last_error() */
   MOE_ERR_NOMEM = 3,
   MOE_ERR_TIMEOUT = 4,     /* a bounded device- or host-side wait ran out */
-  MOE_ERR_SCALE_RANGE = 5, /* an E8M0 scale would push a weight out of fp16 range */
+  MOE_ERR_SCALE_RANGE = 5, /* an E8M0 weight scale byte is 0xFF (NaN) */
   MOE_ERR_STATE = 6,       /* layer not loaded, peers not attached, ... */
   MOE_ERR_NO_SM100 = 7     /* device is not compute capability 10.x */
 };
@@ -80,7 +80,7 @@ int moe_load_layer(moe_handle h, int layer, const uint8_t *w1_codes, const uint8
 int moe_shard_range(int intermediate_dim, int tp_size, int tp_rank, int *start, int *len);
 
 /* moe_forward.flags */
-#define MOE_FWD_SIMT_GEMM 1u    /* run the plain CUDA-core validation GEMM instead of tcgen05 */
+#define MOE_FWD_SIMT_GEMM 1u    /* run the plain CUDA-core validation GEMM (fp16 operands) instead of tcgen05 */
 #define MOE_FWD_PARTIAL_F32 2u  /* TP: leave this rank's fp32 partial in the handle, write no output */
 
 /* Replaces moe_gpu()/moe_gpu_120b() steps 2-8 (getp_run.cpp:2540, :2896): router,
@@ -116,11 +116,23 @@ enum {
   MOE_DBG_PAIR_ROW = 5, /* i32 [rows, K]    local_ids_g */
   MOE_DBG_ROW_TOKEN = 6,/* i32 [rows*K]     expert_row_token_g */
   MOE_DBG_OUT_F32 = 7,  /* f32 [rows, H]    block output before the bf16 rounding (MOE_CFG_KEEP_F32_OUT) */
-  MOE_DBG_STATUS = 8,   /* u32 [1]          device status word */
-  MOE_DBG_HBUF = 9,     /* f16 [rows*K, Dl] SwiGLU output, permuted rows (gate_up_bf16_g) */
+  MOE_DBG_STATUS = 8,   /* u32 [4096]       device status word (first element) and diagnostics */
   MOE_DBG_YBUF = 10     /* f32 [rows*K, H]  MLP2 output, permuted rows (expert_output_partial_g) */
 };
 int moe_get_debug(moe_handle h, int which, void *host_dst, size_t bytes);
+
+/* Per-stage device timing (replaces the reference's TIMER_BLOCK / ProfileManager,
+ * getp-csrc/utils.hpp:48-222, which brackets stages with hipDeviceSynchronize):
+ * while enabled, every moe_forward records CUDA events between its kernels on
+ * the caller's stream.  moe_profile_collect waits for them, adds the elapsed
+ * milliseconds of each stage over all calls since the last collect into
+ * ms[MOE_N_STAGES] and returns the number of calls in *n_calls. */
+enum {
+  MOE_STAGE_ROUTER = 0, MOE_STAGE_TOPK = 1, MOE_STAGE_INDEX = 2, MOE_STAGE_GATHER = 3,
+  MOE_STAGE_MLP1 = 4, MOE_STAGE_MLP2 = 5, MOE_STAGE_COMBINE = 6, MOE_N_STAGES = 7
+};
+int moe_profile_enable(moe_handle h, int on);
+int moe_profile_collect(moe_handle h, float *ms, int *n_calls);
 
 const char *moe_last_error(moe_handle h);
 const char *moe_strerror(int code);
