@@ -3,6 +3,7 @@
 // reference runtime does around its MoE kernels (getp-csrc/getp_run.cpp:
 // malloc_gpu_run_state*, copy_weights_to_gpu_*, moe_gpu / moe_gpu_120b), minus
 // the host synchronisations: nothing in moe_forward() waits for the device.
+#include <algorithm>
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
@@ -168,7 +169,7 @@ int moe_create(const moe_config *cfg, moe_handle *out) {
   if (!cfg || !out) return MOE_ERR_INVALID;
   *out = nullptr;
   if (cfg->hidden_dim <= 0 || cfg->hidden_dim % 32 || cfg->intermediate_dim <= 0 || cfg->intermediate_dim % 32 ||
-      cfg->n_experts <= 0 || cfg->n_experts > 256 || cfg->experts_per_token <= 0 || cfg->experts_per_token > 8 ||
+      cfg->n_experts <= 0 || cfg->n_experts > 256 || (cfg->n_experts & 1) || cfg->experts_per_token <= 0 || cfg->experts_per_token > 8 ||
       cfg->experts_per_token > cfg->n_experts || cfg->n_layers <= 0 || cfg->max_rows <= 0 || cfg->tp_size <= 0 ||
       cfg->tp_rank < 0 || cfg->tp_rank >= cfg->tp_size)
     return MOE_ERR_INVALID;
@@ -197,6 +198,8 @@ int moe_create(const moe_config *cfg, moe_handle *out) {
   int rc;
   if ((rc = dev_alloc(c, &c->t_in, T * c->H))) return rc;
   if ((rc = dev_alloc(c, &c->logits, T * c->E))) return rc;
+  // splits * rows never exceeds (sm_count / tiles) * 64 * tiles = 64 * sm_count
+  if ((rc = dev_alloc(c, &c->router_part, std::max<size_t>(T, 64 * static_cast<size_t>(c->sm_count) + 64) * c->E))) return rc;
   if ((rc = dev_alloc(c, &c->topk_idx, T * c->K))) return rc;
   if ((rc = dev_alloc(c, &c->topk_w, T * c->K))) return rc;
   if ((rc = dev_alloc(c, &c->counts, (size_t)c->E))) return rc;
@@ -255,7 +258,7 @@ int moe_destroy(moe_handle c) {
   for (auto &w : c->layers) free_layer(w);
   for (cudaEvent_t e : c->prof_events) cudaEventDestroy(e);
   for (cudaEvent_t e : c->prof_pool) cudaEventDestroy(e);
-  cudaFree(c->t_in); cudaFree(c->logits); cudaFree(c->topk_idx); cudaFree(c->topk_w); cudaFree(c->counts);
+  cudaFree(c->t_in); cudaFree(c->logits); cudaFree(c->router_part); cudaFree(c->topk_idx); cudaFree(c->topk_w); cudaFree(c->counts);
   cudaFree(c->offsets); cudaFree(c->pair_row); cudaFree(c->row_token); cudaFree(c->xperm); cudaFree(c->hbuf);
   cudaFree(c->ybuf); cudaFree(c->out_f32); cudaFree(c->out_bf16); cudaFree(c->work1); cudaFree(c->work2);
   cudaFree(c->n_work); cudaFree(c->status);
@@ -353,7 +356,8 @@ int moe_load_layer(moe_handle c, int layer, const uint8_t *w1_codes, const uint8
 int moe_route_topk(moe_handle c, const float *logits_dev, int rows, int *idx_dev, float *w_dev, void *stream) {
   if (!c || !logits_dev || !idx_dev || !w_dev || rows <= 0) return MOE_ERR_INVALID;
   CU_TRY(c, cudaSetDevice(c->cfg.device));
-  launch_topk_softmax(logits_dev, rows, c->E, c->K, idx_dev, w_dev, nullptr, static_cast<cudaStream_t>(stream));
+  launch_topk_softmax(const_cast<float *>(logits_dev), nullptr, 0, nullptr, rows, c->E, c->K, idx_dev, w_dev, nullptr,
+                      static_cast<cudaStream_t>(stream));
   c->launches += 1;
   CU_TRY(c, cudaGetLastError());
   return MOE_OK;
@@ -382,9 +386,10 @@ int moe_forward(moe_handle c, int layer, const void *t_dev, int rows, void *out_
     c->prof_events.push_back(ev);
   };
   mark();
-  launch_router_logits(t, w.router_w3, w.router_b, c->logits, T, H, E, s);
+  const int splits = router_splits(T, H, c->sm_count);
+  launch_router_partials(t, w.router_w3, c->router_part, T, H, E, splits, s);
   mark();
-  launch_topk_softmax(c->logits, T, E, K, c->topk_idx, c->topk_w, c->counts, s);
+  launch_topk_softmax(c->logits, c->router_part, splits, w.router_b, T, E, K, c->topk_idx, c->topk_w, c->counts, s);
   mark();
   launch_build_index(c->topk_idx, c->counts, T, E, K, n_nt1, n_nt2, c->offsets, c->tile_base, c->pair_row,
                      c->row_token, c->work1, c->work2, c->n_work, c->max_work1, c->max_work2, c->status, s);

@@ -95,6 +95,7 @@ struct moe_ctx {
   // run state (names of the reference's GPURunState fields in comments)
   __nv_bfloat16 *t_in = nullptr;    // gather_x_g          [max_rows, H]
   float *logits = nullptr;          // router_score_g      [max_rows, E]
+  float *router_part = nullptr;     // split-k partial sums of the router [splits, rows, E]
   int *topk_idx = nullptr;          // topk_i_g            [max_rows, K]
   float *topk_w = nullptr;          // topk_v_g            [max_rows, K]
   int *counts = nullptr;            // d_expert_counts     [E]
@@ -130,10 +131,11 @@ struct moe_ctx {
 namespace moe {
 
 // route.cu
-void launch_router_logits(const __nv_bfloat16 *t, const __nv_bfloat16 *w3, const float *bias, float *logits,
-                          int T, int H, int E, cudaStream_t s);
-void launch_topk_softmax(const float *logits, int T, int E, int K, int *idx, float *w, int *counts,
-                         cudaStream_t s);
+int router_splits(int T, int H, int sm_count);
+void launch_router_partials(const __nv_bfloat16 *t, const __nv_bfloat16 *w3, float *partial, int T, int H, int E,
+                            int splits, cudaStream_t s);
+void launch_topk_softmax(float *logits, const float *partial, int splits, const float *bias, int T, int E, int K,
+                         int *idx, float *w, int *counts, cudaStream_t s);
 void launch_build_index(const int *topk_idx, const int *counts, int T, int E, int K, int n_ntiles1, int n_ntiles2,
                         int *offsets, int *tile_base, int *pair_row, int *row_token, WorkItem *work1,
                         WorkItem *work2, int *n_work, int max_work1, int max_work2, unsigned int *status,

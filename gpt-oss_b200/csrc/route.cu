@@ -14,16 +14,24 @@ namespace moe {
 // Router logits: logits[t, e] = sum_k t[t, k] * Wr[e, k] + br[e], fp32.
 // Reference: matmul + bias of run.cpp:660-669 (double accumulation of float
 // products); the reference GPU path rounds the logits to bf16
-// (getp_run.cpp:2612-2620), which this kernel deliberately does not.
+// (getp_run.cpp:2612-2620), which this path deliberately does not.
 //
 // The fp32 router weight is pre-split at load time into three bf16 planes
 // (hi + mid + lo == w exactly, 8+8+8 significand bits), so each plane times a
 // bf16 activation is an exact fp32 product and the sum runs on the tensor
-// cores (mma.sync m16n8k16, fp32 accumulate).  A block owns 16 tokens x 64
-// experts; its 8 warps split the k16 steps and their partial sums are added
-// in a fixed order in double precision.
+// cores (mma.sync m16n8k16, fp32 accumulate).  A block owns 64 tokens x up to
+// 128 experts x one slice of k (split-k keeps all SMs busy at decode batch
+// sizes); operands are staged through shared memory with cp.async, double
+// buffered.  Each slice writes its partial sums; topk_softmax_kernel adds the
+// slices in a fixed order in double precision, so results do not depend on
+// scheduling.
 // ---------------------------------------------------------------------------
-constexpr int kRtTok = 16, kRtExp = 64, kRtWarps = 8;
+constexpr int kRtTok = 64, kRtExp = 128, kRtK = 64, kRtThreads = 256;
+constexpr int kRtPitch = kRtK * 2 + 16;                 // bytes per staged row: 64 bf16 + pad (no bank conflicts)
+constexpr int kRtXBytes = kRtTok * kRtPitch;            // 9216
+constexpr int kRtWBytes = 3 * kRtExp * kRtPitch;        // 55296
+constexpr int kRtStage = kRtXBytes + kRtWBytes;         // 64512
+constexpr int kRtSmem = 2 * kRtStage;                   // 129024
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -31,74 +39,109 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, bool valid) {
+  const int sz = valid ? 16 : 0;  // size 0: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
+}
 
-__global__ void __launch_bounds__(kRtWarps * 32)
-router_logits_kernel(const __nv_bfloat16 *__restrict__ t, const __nv_bfloat16 *__restrict__ w3,
-                     const float *__restrict__ bias, float *__restrict__ logits, int T, int H, int E) {
-  __shared__ float part[kRtWarps][kRtTok][kRtExp + 1];
+// partial[(split * T + tok) * E + e]
+__global__ void __launch_bounds__(kRtThreads)
+router_partial_kernel(const __nv_bfloat16 *__restrict__ t, const __nv_bfloat16 *__restrict__ w3,
+                      float *__restrict__ partial, int T, int H, int E, int chunks_per_split) {
+  extern __shared__ __align__(16) uint8_t rt_smem[];
+  const uint32_t sbase = static_cast<uint32_t>(__cvta_generic_to_shared(rt_smem));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, q = lane & 3;
-  const int tok0 = blockIdx.x * kRtTok, e0 = blockIdx.y * kRtExp;
+  const int tok0 = blockIdx.x * kRtTok, e0 = blockIdx.z * kRtExp;
+  const int n_chunks = H / kRtK + ((H % kRtK) ? 1 : 0);
+  const int c_begin = blockIdx.y * chunks_per_split, c_end = min(n_chunks, c_begin + chunks_per_split);
   const size_t plane = static_cast<size_t>(E) * H;
+  const int mt = warp & 3, nh = warp >> 2;  // 16-token tile, 64-expert half
 
-  float acc[kRtExp / 8][4];
+  float acc[8][4];
 #pragma unroll
-  for (int n = 0; n < kRtExp / 8; ++n)
+  for (int n = 0; n < 8; ++n)
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
 
-  const int r0 = tok0 + g, r1 = tok0 + g + 8;
-  const uint32_t *x0 = reinterpret_cast<const uint32_t *>(t + static_cast<size_t>(min(r0, T - 1)) * H);
-  const uint32_t *x1 = reinterpret_cast<const uint32_t *>(t + static_cast<size_t>(min(r1, T - 1)) * H);
-  const bool v0 = r0 < T, v1 = r1 < T;
+  auto issue = [&](int chunk, int buf) {
+    const int k0 = chunk * kRtK;
+    const uint32_t xs = sbase + buf * kRtStage, ws = xs + kRtXBytes;
+    // 8 x 16-byte pieces per row
+    for (int i = threadIdx.x; i < kRtTok * 8; i += kRtThreads) {
+      const int r = i >> 3, p = i & 7;
+      const bool ok = (tok0 + r < T) && (k0 + p * 8 < H);
+      cp_async16(xs + r * kRtPitch + p * 16, t + static_cast<size_t>(min(tok0 + r, T - 1)) * H + min(k0 + p * 8, H - 8), ok);
+    }
+    for (int i = threadIdx.x; i < 3 * kRtExp * 8; i += kRtThreads) {
+      const int pl = i / (kRtExp * 8), rem = i % (kRtExp * 8), r = rem >> 3, p = rem & 7;
+      const bool ok = (e0 + r < E) && (k0 + p * 8 < H);
+      cp_async16(ws + (pl * kRtExp + r) * kRtPitch + p * 16,
+                 w3 + pl * plane + static_cast<size_t>(min(e0 + r, E - 1)) * H + min(k0 + p * 8, H - 8), ok);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
 
-  for (int ks = warp; ks < H / 16; ks += kRtWarps) {
-    const int kw = ks * 8 + q;  // 32-bit word index of (k0 + 2q)
-    uint32_t a[4];
-    a[0] = v0 ? __ldg(x0 + kw) : 0u;
-    a[1] = v1 ? __ldg(x1 + kw) : 0u;
-    a[2] = v0 ? __ldg(x0 + kw + 4) : 0u;
-    a[3] = v1 ? __ldg(x1 + kw + 4) : 0u;
+  if (c_begin < c_end) issue(c_begin, 0);
+  for (int c = c_begin; c < c_end; ++c) {
+    const int buf = (c - c_begin) & 1;
+    if (c + 1 < c_end) {
+      issue(c + 1, buf ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const uint8_t *xs = rt_smem + buf * kRtStage, *ws = xs + kRtXBytes;
 #pragma unroll
-    for (int n = 0; n < kRtExp / 8; ++n) {
-      const int e = e0 + n * 8 + g;
-      if (e0 + n * 8 >= E) break;
-      const bool ve = e < E;
-      const uint32_t *wrow = reinterpret_cast<const uint32_t *>(w3 + static_cast<size_t>(min(e, E - 1)) * H);
+    for (int ks = 0; ks < kRtK / 16; ++ks) {
+      const int kb = ks * 32 + q * 4;  // byte offset of (k0 + 16 ks + 2q) in a staged row
+      uint32_t a[4];
+      const uint8_t *xr = xs + (mt * 16 + g) * kRtPitch + kb;
+      a[0] = *reinterpret_cast<const uint32_t *>(xr);
+      a[1] = *reinterpret_cast<const uint32_t *>(xr + 8 * kRtPitch);
+      a[2] = *reinterpret_cast<const uint32_t *>(xr + 16);
+      a[3] = *reinterpret_cast<const uint32_t *>(xr + 8 * kRtPitch + 16);
 #pragma unroll
-      for (int p = 0; p < 3; ++p) {
-        const uint32_t *wp = wrow + p * (plane / 2);
-        const uint32_t b0 = ve ? __ldg(wp + kw) : 0u;
-        const uint32_t b1 = ve ? __ldg(wp + kw + 4) : 0u;
-        mma_bf16_16816(acc[n], a, b0, b1);
+      for (int n = 0; n < 8; ++n) {
+#pragma unroll
+        for (int pl = 0; pl < 3; ++pl) {
+          const uint8_t *wr = ws + (pl * kRtExp + nh * 64 + n * 8 + g) * kRtPitch + kb;
+          mma_bf16_16816(acc[n], a, *reinterpret_cast<const uint32_t *>(wr), *reinterpret_cast<const uint32_t *>(wr + 16));
+        }
       }
     }
+    __syncthreads();
   }
+  float *out = partial + static_cast<size_t>(blockIdx.y) * T * E;
 #pragma unroll
-  for (int n = 0; n < kRtExp / 8; ++n) {
-    part[warp][g][n * 8 + 2 * q] = acc[n][0];
-    part[warp][g][n * 8 + 2 * q + 1] = acc[n][1];
-    part[warp][g + 8][n * 8 + 2 * q] = acc[n][2];
-    part[warp][g + 8][n * 8 + 2 * q + 1] = acc[n][3];
-  }
-  __syncthreads();
-  for (int i = threadIdx.x; i < kRtTok * kRtExp; i += blockDim.x) {
-    const int r = i / kRtExp, c = i % kRtExp;
-    const int tok = tok0 + r, e = e0 + c;
-    if (tok >= T || e >= E) continue;
-    double s = 0.0;
-#pragma unroll
-    for (int w = 0; w < kRtWarps; ++w) s += static_cast<double>(part[w][r][c]);
-    float v = static_cast<float>(s);
-    v = __fadd_rn(v, bias[e]);  // run.cpp:667-669: bias added in float after the matmul
-    logits[static_cast<size_t>(tok) * E + e] = v;
+  for (int n = 0; n < 8; ++n) {
+    const int e = e0 + nh * 64 + n * 8 + 2 * q;
+    const int r0 = tok0 + mt * 16 + g, r1 = r0 + 8;
+    if (e < E) {  // E is even (checked by the launcher), so e + 1 < E as well
+      if (r0 < T) *reinterpret_cast<float2 *>(out + static_cast<size_t>(r0) * E + e) = make_float2(acc[n][0], acc[n][1]);
+      if (r1 < T) *reinterpret_cast<float2 *>(out + static_cast<size_t>(r1) * E + e) = make_float2(acc[n][2], acc[n][3]);
+    }
   }
 }
 
-void launch_router_logits(const __nv_bfloat16 *t, const __nv_bfloat16 *w3, const float *bias, float *logits,
-                          int T, int H, int E, cudaStream_t s) {
-  dim3 grid((T + kRtTok - 1) / kRtTok, (E + kRtExp - 1) / kRtExp);
-  router_logits_kernel<<<grid, kRtWarps * 32, 0, s>>>(t, w3, bias, logits, T, H, E);
+int router_splits(int T, int H, int sm_count) {
+  const int tiles = (T + kRtTok - 1) / kRtTok, n_chunks = (H + kRtK - 1) / kRtK;
+  int splits = max(1, min(min(16, n_chunks), sm_count / tiles));
+  const int cps = (n_chunks + splits - 1) / splits;
+  return (n_chunks + cps - 1) / cps;  // every split gets at least one chunk
+}
+
+void launch_router_partials(const __nv_bfloat16 *t, const __nv_bfloat16 *w3, float *partial, int T, int H, int E,
+                            int splits, cudaStream_t s) {
+  static bool attr = false;
+  if (!attr) {
+    cudaFuncSetAttribute(router_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRtSmem);
+    attr = true;
+  }
+  const int n_chunks = (H + kRtK - 1) / kRtK, cps = (n_chunks + splits - 1) / splits;
+  dim3 grid((T + kRtTok - 1) / kRtTok, splits, (E + kRtExp - 1) / kRtExp);
+  router_partial_kernel<<<grid, kRtThreads, kRtSmem, s>>>(t, w3, partial, T, H, E, cps);
 }
 
 // ---------------------------------------------------------------------------
@@ -112,18 +155,34 @@ void launch_router_logits(const __nv_bfloat16 *t, const __nv_bfloat16 *w3, const
 constexpr int kMaxExpPerLane = 8;  // E <= 256
 constexpr int kMaxTopK = 8;
 
-__global__ void topk_softmax_kernel(const float *__restrict__ logits, int T, int E, int K, int *__restrict__ idx,
+// With `partial` set, the logits are first formed from the router's split-k partial sums: slices added
+// in ascending order in double precision, rounded to float, then the bias added in float
+// (run.cpp:662-669), and written to `logits`.  Otherwise `logits` is the input.
+__global__ void topk_softmax_kernel(float *__restrict__ logits, const float *__restrict__ partial, int splits,
+                                    const float *__restrict__ bias, int T, int E, int K, int *__restrict__ idx,
                                     float *__restrict__ w, int *__restrict__ counts) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= T) return;
-  const float *row = logits + static_cast<size_t>(warp) * E;
+  float *row = logits + static_cast<size_t>(warp) * E;
   float v[kMaxExpPerLane];
   unsigned taken = 0;
 #pragma unroll
   for (int i = 0; i < kMaxExpPerLane; ++i) {
     const int e = lane + 32 * i;
-    v[i] = e < E ? row[e] : 0.f;
-    if (e >= E) taken |= 1u << i;
+    if (e < E) {
+      if (partial != nullptr) {
+        double sum = 0.0;
+        for (int sp = 0; sp < splits; ++sp)
+          sum += static_cast<double>(partial[(static_cast<size_t>(sp) * T + warp) * E + e]);
+        v[i] = __fadd_rn(static_cast<float>(sum), bias[e]);
+        row[e] = v[i];
+      } else {
+        v[i] = row[e];
+      }
+    } else {
+      v[i] = 0.f;
+      taken |= 1u << i;
+    }
   }
   float sel_v = 0.f;  // lane k keeps the k-th selected logit
   int sel_i = 0;
@@ -161,11 +220,11 @@ __global__ void topk_softmax_kernel(const float *__restrict__ logits, int T, int
   }
 }
 
-void launch_topk_softmax(const float *logits, int T, int E, int K, int *idx, float *w, int *counts,
-                         cudaStream_t s) {
+void launch_topk_softmax(float *logits, const float *partial, int splits, const float *bias, int T, int E, int K,
+                         int *idx, float *w, int *counts, cudaStream_t s) {
   const int threads = 128;
   const int blocks = (T * 32 + threads - 1) / threads;
-  topk_softmax_kernel<<<blocks, threads, 0, s>>>(logits, T, E, K, idx, w, counts);
+  topk_softmax_kernel<<<blocks, threads, 0, s>>>(logits, partial, splits, bias, T, E, K, idx, w, counts);
 }
 
 // ---------------------------------------------------------------------------

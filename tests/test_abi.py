@@ -1,0 +1,74 @@
+"""CPU-side checks of the C-ABI library: it loads, exports every symbol the
+header declares, and its host-only entry points behave.  No kernel is launched."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from conftest import ROOT
+
+
+def declared_functions():
+    text = open(os.path.join(ROOT, "include", "moe_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(moe_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(pkg):
+    lib = pkg.lib()
+    names = declared_functions()
+    assert len(names) >= 15
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/moe_b200.h but not exported"
+    assert set(pkg.EXPORTS) <= set(names)
+
+
+def test_shard_ranges_are_32_aligned_and_cover(pkg):
+    for D, tp in [(2880, 1), (2880, 2), (2880, 4), (2880, 8), (96, 3), (64, 2)]:
+        pos = 0
+        lens = []
+        for r in range(tp):
+            s, n = pkg.shard_range(D, tp, r)
+            assert s == pos and s % 32 == 0 and n % 32 == 0 and n > 0
+            pos += n
+            lens.append(n)
+        assert pos == D
+        assert max(lens) - min(lens) <= 32
+    assert [pkg.shard_range(2880, 4, r)[1] for r in range(4)] == [736, 736, 704, 704]
+    with pytest.raises(pkg.MoeError):
+        pkg.shard_range(2880, 4, 4)
+    with pytest.raises(pkg.MoeError):
+        pkg.shard_range(100, 2, 0)   # not a multiple of 32
+
+
+def test_create_rejects_bad_config_and_fails_loudly_without_gpu(pkg):
+    lib = pkg.lib()
+    h = C.c_void_p()
+    bad = pkg.MoeConfig(2880, 2880, 128, 4, 1, 7.0, 1.702, 0, 1, 0, 0, 0)      # max_rows = 0
+    assert lib.moe_create(C.byref(bad), C.byref(h)) == 1 and not h
+    bad = pkg.MoeConfig(2880, 2890, 128, 4, 1, 7.0, 1.702, 64, 1, 0, 0, 0)     # D % 32 != 0
+    assert lib.moe_create(C.byref(bad), C.byref(h)) == 1 and not h
+    bad = pkg.MoeConfig(2880, 2880, 128, 4, 1, 7.0, 1.702, 64, 2, 2, 0, 0)     # rank outside group
+    assert lib.moe_create(C.byref(bad), C.byref(h)) == 1 and not h
+    import torch
+    if not torch.cuda.is_available():
+        # no CPU path exists: creation must fail with a CUDA error, not fall back
+        with pytest.raises(pkg.MoeError) as ei:
+            pkg.MoeBlock(64, 64, 8, max_rows=8)
+        assert ei.value.code in (2, 7)
+
+
+def test_error_strings(pkg):
+    lib = pkg.lib()
+    assert lib.moe_strerror(0) == b"ok"
+    assert b"wait" in lib.moe_strerror(4)
+    assert lib.moe_last_error(None) == b"null handle"
+
+
+def test_algorithmic_work_matches_published_formula(synth):
+    # 199 065 600 flop per token + router; bytes = experts * 13 236 480 + rows in/out + router weights
+    flops, nbytes = synth.algorithmic_work(1856, 2880, 2880, 128, 4, 128)
+    assert flops == 1856 * (199065600 + 2 * 2880 * 128)
+    assert synth.weight_bytes_per_expert(2880, 2880) == 13236480
+    assert nbytes == 128 * 13236480 + 1856 * 2880 * 4 + 128 * 2880 * 4
