@@ -40,6 +40,9 @@ METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
 SHAPE = dict(E=128, H=2880, D=2880, K=4)
 CPU_SAMPLE_TOKENS = 32
+# dram read+write bytes / algorithmic bytes of the MLP1 kernel, from the ncu capture summarised in
+# profiles/expert_gemm_mxf8f6f4_20bshape_t464.md (small case; traffic is proportional to the weights streamed)
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.015
 
 
 def workload_config(tokens: int, n_gpus: int) -> dict:
@@ -69,7 +72,7 @@ class ClockSampler:
 
     def __init__(self, uuid: str | None):
         self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
-        cmd = ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"]
+        cmd = ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20"]
         if uuid:
             cmd += ["-i", uuid]
         try:
@@ -136,7 +139,7 @@ def cpu_reference_arm(layer, tokens_bits, steps: int, warmup: int):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=1856)
@@ -275,7 +278,9 @@ def main():
         "clocks": clocks,
         "roofline": {"kernel": "expert_gemm_kernel<1> (MLP1 grouped GEMM + SwiGLU)", "bound": "hbm",
                      "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                     "traffic": None, "peak_source": peak_kind, "bytes_per_launch": mlp1_bytes,
+                     "traffic": mlp1_bytes * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE,
+                     "traffic_source": "ncu capture of a 4x smaller case scaled by bytes processed",
+                     "peak_source": peak_kind, "bytes_per_launch": mlp1_bytes,
                      "ms_per_launch": mlp1_s * 1e3,
                      "tensor_tflops": mlp1_flops / mlp1_s / 1e12, "tensor_peak_tflops": tc_peak,
                      "tensor_frac": mlp1_flops / mlp1_s / 1e12 / tc_peak},

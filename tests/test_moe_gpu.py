@@ -242,3 +242,36 @@ def test_device_pointer_api_and_errors(pkg, synth, port):
         assert ei.value.code == 5
     finally:
         blk.close()
+
+
+@pytest.mark.parametrize("tp", [2, 4])
+def test_tp_shard_partials_sum_to_full_block(tp, pkg, synth, port):
+    """Tensor-parallel shards of the intermediate dimension (one handle per rank, here all on
+    one GPU): every rank routes identically, and the ranks' fp32 partial outputs add up to the
+    unsharded block (MLP2 bias contributed by rank 0 only)."""
+    E, H, D, T = 8, 256, 320, 90          # 320 = 10 scale blocks: uneven 32-aligned shards for tp 4
+    layer = synth.make_layer(E, H, D, seed=55)
+    tokens = synth.make_tokens(T, H, seed=56)
+    _, ref_i, _, ref_out = port.moe_layer(layer, tokens)
+    total = np.zeros((T, H), dtype=np.float64)
+    covered = 0
+    for r in range(tp):
+        blk = pkg.MoeBlock(H, D, E, max_rows=T, tp_size=tp, tp_rank=r, keep_f32=True)
+        try:
+            assert blk.d0 == covered
+            covered += blk.Dl
+            blk.load_layer(0, layer)
+            out = blk.forward_host(0, tokens)        # bf16 of the partial; the fp32 partial is kept too
+            assert np.array_equal(blk.debug(pkg.DBG_TOPK_IDX), ref_i)
+            part = blk.debug(pkg.DBG_OUT_F32).astype(np.float64)
+            d0, d1 = blk.d0, blk.d0 + blk.Dl
+            _, _, _, ref_part = port.moe_layer(layer, tokens, shard=(d0, d1), add_b2=(r == 0))
+            rms = max(1.0, float(np.sqrt((ref_part.astype(np.float64) ** 2).mean())))
+            assert np.abs(part - ref_part).max() <= 1e-2 * rms
+            total += part
+        finally:
+            blk.close()
+    assert covered == D
+    err = np.abs(total - ref_out)
+    assert err.mean() / np.abs(ref_out).mean() <= 5e-3
+    assert err.max() <= 1e-2 * max(1.0, float(np.sqrt((ref_out.astype(np.float64) ** 2).mean())))
