@@ -33,6 +33,7 @@ EXPORTS = [
     "moe_create", "moe_destroy", "moe_load_layer", "moe_shard_range", "moe_forward", "moe_forward_host",
     "moe_synchronize", "moe_host_alloc", "moe_host_free", "moe_route_topk", "moe_get_debug",
     "moe_last_error", "moe_strerror", "moe_launch_count", "moe_profile_enable", "moe_profile_collect",
+    "moe_route_static",
 ]
 STAGES = ("router", "topk", "index", "gather", "mlp1", "mlp2", "combine")
 
@@ -79,6 +80,8 @@ def lib() -> C.CDLL:
         L.moe_strerror.restype = C.c_char_p
         L.moe_launch_count.argtypes = [C.c_void_p]
         L.moe_launch_count.restype = C.c_longlong
+        L.moe_route_static.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
+                                       C.c_void_p]
         L.moe_profile_enable.argtypes = [C.c_void_p, C.c_int]
         L.moe_profile_collect.argtypes = [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_int)]
         _lib = L
@@ -173,6 +176,12 @@ class MoeBlock:
     def route_topk(self, logits_ptr: int, rows: int, idx_ptr: int, w_ptr: int, stream: int = 0):
         self._check(self.L.moe_route_topk(self.h, C.c_void_p(logits_ptr), rows, C.c_void_p(idx_ptr),
                                           C.c_void_p(w_ptr), C.c_void_p(stream)))
+
+    def route_static(self, layer: int, t_ptr: int, rows: int, logits_ptr: int, idx_ptr: int, w_ptr: int,
+                     stream: int = 0):
+        """Router + top-k + softmax with the library's fixed scratch array; allocates nothing."""
+        self._check(self.L.moe_route_static(self.h, layer, C.c_void_p(t_ptr), rows, C.c_void_p(logits_ptr),
+                                            C.c_void_p(idx_ptr), C.c_void_p(w_ptr), C.c_void_p(stream)))
 
     def debug(self, which: int) -> np.ndarray:
         T, E, K, H = self.rows, self.E, self.K, self.H

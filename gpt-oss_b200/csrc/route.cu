@@ -6,6 +6,9 @@
 // by build_index_kernel.
 #include <cuda_fp8.h>
 
+#include <cstdio>
+#include <mutex>
+
 #include "moe_internal.cuh"
 
 namespace moe {
@@ -505,4 +508,86 @@ void launch_combine(const float *y, const int *topk_idx, const float *topk_w, co
   combine_kernel<<<T, 256, 0, s>>>(y, topk_idx, topk_w, pair_row, T, H, K, out_bf16, out_f32);
 }
 
+// ---------------------------------------------------------------------------
+// Routing without any allocation (no counterpart in the reference).
+//
+// Who this is for: a caller that is not allowed to reach the CUDA allocator at
+// the moment it needs a routing decision.  Two examples: a serving loop that
+// was given all of its device memory once, at start-up, by a pool that owns the
+// rest of the GPU, so that a later cudaMalloc can fail or fragment that pool;
+// and a latency-critical thread for which the device-wide synchronisation
+// hidden inside cudaMalloc/cudaFree would stall work on other streams.
+//
+// The router needs scratch memory for its split-k partial sums.  Here that
+// scratch is a fixed array in the library's own device image instead of a
+// cudaMalloc'ed buffer: 8 MiB, which every GPU that loads this library holds
+// until the process exits.  Host code cannot use the array's name as a device
+// address; its address is looked up once per device, with that device current,
+// by cudaGetSymbolAddress on the first call made on that device.  That first
+// call should therefore be made during start-up, before any stream capture.
+//
+// All calls share the one array per device, so two calls whose kernels overlap
+// on the GPU (different streams) race; serialise them.  Nothing in the array
+// has to start at zero: every element a call reads was written by the same call
+// (each k-slice writes its full rows x experts block), so stale contents of an
+// earlier, larger call are never read.
+// ---------------------------------------------------------------------------
+constexpr size_t kStaticRouteFloats = static_cast<size_t>(2) << 20;  // 2 Mi floats = 8 MiB
+static __device__ __align__(256) float g_route_scratch[kStaticRouteFloats];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float *g_route_scratch_ptr[kMaxDevices] = {};
+std::mutex g_route_scratch_mu;
+
+// Device address of g_route_scratch on `device`, which must be the current device.
+cudaError_t route_scratch_for(int device, float **out) {
+  std::lock_guard<std::mutex> lock(g_route_scratch_mu);
+  if (g_route_scratch_ptr[device] == nullptr) {
+    float *p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_route_scratch);
+    if (e != cudaSuccess) return e;
+    g_route_scratch_ptr[device] = p;
+  }
+  *out = g_route_scratch_ptr[device];
+  return cudaSuccess;
+}
+}  // namespace
+
 }  // namespace moe
+
+extern "C" int moe_route_static(moe_handle c, int layer, const void *t_dev, int rows, float *logits_dev,
+                                int *idx_dev, float *w_dev, void *stream) {
+  using namespace moe;
+  if (!c) return MOE_ERR_INVALID;
+  auto fail = [&](int code, const char *msg) { c->err = msg; return code; };
+  if (layer < 0 || layer >= c->L || !t_dev || !logits_dev || !idx_dev || !w_dev || rows <= 0)
+    return fail(MOE_ERR_INVALID, "moe_route_static: bad layer index, null pointer or rows <= 0");
+  if (c->cfg.device < 0 || c->cfg.device >= kMaxDevices) return fail(MOE_ERR_INVALID, "moe_route_static: device ordinal out of range");
+  LayerWeights &w = c->layers[layer];
+  if (!w.loaded) return fail(MOE_ERR_STATE, "moe_route_static: layer has no weights");
+  const size_t per_slice = static_cast<size_t>(rows) * c->E;
+  if (per_slice > kStaticRouteFloats) {
+    char buf[200];
+    snprintf(buf, sizeof(buf), "moe_route_static: rows * n_experts = %zu exceeds the fixed scratch of %zu floats (8 MiB)",
+             per_slice, kStaticRouteFloats);
+    return fail(MOE_ERR_INVALID, buf);
+  }
+  if (cudaSetDevice(c->cfg.device) != cudaSuccess) return fail(MOE_ERR_CUDA, "moe_route_static: cudaSetDevice failed");
+  float *scratch = nullptr;
+  if (route_scratch_for(c->cfg.device, &scratch) != cudaSuccess)
+    return fail(MOE_ERR_CUDA, "moe_route_static: cudaGetSymbolAddress failed");
+  // as many k-slices as the regular path would use, but no more than fit the fixed scratch
+  int splits = router_splits(rows, c->H, c->sm_count);
+  const int fit = static_cast<int>(kStaticRouteFloats / per_slice);
+  if (splits > fit) {
+    const int n_chunks = (c->H + kRtK - 1) / kRtK, cps = (n_chunks + fit - 1) / fit;
+    splits = (n_chunks + cps - 1) / cps;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  launch_router_partials(static_cast<const __nv_bfloat16 *>(t_dev), w.router_w3, scratch, rows, c->H, c->E, splits, s);
+  launch_topk_softmax(logits_dev, scratch, splits, w.router_b, rows, c->E, c->K, idx_dev, w_dev, nullptr, s);
+  c->launches += 2;
+  if (cudaGetLastError() != cudaSuccess) return fail(MOE_ERR_CUDA, "moe_route_static: kernel launch failed");
+  return MOE_OK;
+}

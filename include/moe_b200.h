@@ -106,6 +106,19 @@ void moe_host_free(void *p);
  * pointers).  Replaces run_route_select_softmax_fused (kernels/moe.hpp:565-599). */
 int moe_route_topk(moe_handle h, const float *logits_dev, int rows, int *idx_dev, float *w_dev, void *stream);
 
+/* No counterpart in the reference.  Router + top-k + softmax for a caller that must not reach
+ * the CUDA allocator when it needs a routing decision (its memory was handed out once by a pool
+ * that owns the device, or it cannot afford the device-wide synchronisation inside cudaMalloc).
+ * The split-k scratch of the router lives in a fixed 8 MiB array inside the library's device image
+ * (held by every GPU that loads the library until the process exits); the call allocates nothing.
+ * t_dev: bf16 [rows, H] normalised rows; outputs, all caller-owned device memory: logits_dev fp32
+ * [rows, E], idx_dev i32 [rows, K], w_dev fp32 [rows, K].  Limit: rows * n_experts <= 2 097 152
+ * (MOE_ERR_INVALID beyond it).  The first call on a device looks up the array's device address and
+ * should be made at start-up, before any stream capture.  All calls on a device share the array:
+ * calls whose kernels overlap on the GPU race.  Stream-ordered on `stream`. */
+int moe_route_static(moe_handle h, int layer, const void *t_dev, int rows, float *logits_dev, int *idx_dev,
+                     float *w_dev, void *stream);
+
 /* Intermediate results of the last forward, copied to host memory. */
 enum {
   MOE_DBG_LOGITS = 0,   /* f32 [rows, E]    router_score_g */
