@@ -27,14 +27,17 @@ FWD_SIMT_GEMM = 1
 FWD_PARTIAL_F32 = 2
 
 DBG_LOGITS, DBG_TOPK_IDX, DBG_TOPK_W, DBG_COUNTS, DBG_OFFSETS, DBG_PAIR_ROW, DBG_ROW_TOKEN, DBG_OUT_F32, \
-    DBG_STATUS, DBG_HBUF, DBG_YBUF = range(11)
+    DBG_STATUS, DBG_HBUF, DBG_YBUF, DBG_GATHER = range(12)
 
 EXPORTS = [
     "moe_create", "moe_destroy", "moe_load_layer", "moe_shard_range", "moe_forward", "moe_forward_host",
     "moe_synchronize", "moe_host_alloc", "moe_host_free", "moe_route_topk", "moe_get_debug",
     "moe_last_error", "moe_strerror", "moe_launch_count", "moe_profile_enable", "moe_profile_collect",
-    "moe_route_static",
+    "moe_route_static", "moe_tp_export", "moe_tp_attach_ipc", "moe_tp_buffer", "moe_tp_attach_ptr",
+    "moe_tp_forward", "moe_tp_allgather", "moe_tp_reduce_scatter",
 ]
+TP_BUF_GATHER, TP_BUF_PARTIAL, TP_BUF_FLAGS = 0, 1, 2
+TP_HANDLE_BYTES = 64
 STAGES = ("router", "topk", "index", "gather", "mlp1", "mlp2", "combine")
 
 
@@ -82,6 +85,13 @@ def lib() -> C.CDLL:
         L.moe_launch_count.restype = C.c_longlong
         L.moe_route_static.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
                                        C.c_void_p]
+        L.moe_tp_export.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
+        L.moe_tp_attach_ipc.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+        L.moe_tp_buffer.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_void_p)]
+        L.moe_tp_attach_ptr.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int]
+        L.moe_tp_forward.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_uint, C.c_void_p]
+        L.moe_tp_allgather.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+        L.moe_tp_reduce_scatter.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
         L.moe_profile_enable.argtypes = [C.c_void_p, C.c_int]
         L.moe_profile_collect.argtypes = [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_int)]
         _lib = L
@@ -183,13 +193,47 @@ class MoeBlock:
         self._check(self.L.moe_route_static(self.h, layer, C.c_void_p(t_ptr), rows, C.c_void_p(logits_ptr),
                                             C.c_void_p(idx_ptr), C.c_void_p(w_ptr), C.c_void_p(stream)))
 
+    # ---- tensor-parallel group -------------------------------------------------------------
+    def tp_export_all(self) -> bytes:
+        """The IPC handles of this rank's three symmetric buffers, 3 x 64 bytes."""
+        out = b""
+        for which in (TP_BUF_GATHER, TP_BUF_PARTIAL, TP_BUF_FLAGS):
+            buf = C.create_string_buffer(TP_HANDLE_BYTES)
+            self._check(self.L.moe_tp_export(self.h, which, buf))
+            out += buf.raw
+        return out
+
+    def tp_attach_all(self, rank: int, blob: bytes):
+        """Attaches rank `rank`'s buffers from the 192 bytes its tp_export_all() returned."""
+        assert len(blob) == 3 * TP_HANDLE_BYTES
+        for which in (TP_BUF_GATHER, TP_BUF_PARTIAL, TP_BUF_FLAGS):
+            part = blob[which * TP_HANDLE_BYTES:(which + 1) * TP_HANDLE_BYTES]
+            self._check(self.L.moe_tp_attach_ipc(self.h, which, rank, C.c_char_p(part)))
+
+    def tp_buffer(self, which: int) -> int:
+        p = C.c_void_p()
+        self._check(self.L.moe_tp_buffer(self.h, which, C.byref(p)))
+        return p.value
+
+    def tp_forward(self, layer: int, t_ptr: int, rows_local: int, out_ptr: int, flags: int = 0, stream: int = 0):
+        self._check(self.L.moe_tp_forward(self.h, layer, C.c_void_p(t_ptr), rows_local, C.c_void_p(out_ptr), flags,
+                                          C.c_void_p(stream)))
+        self.rows = rows_local * self.cfg.tp_size
+
+    def tp_allgather(self, src_ptr: int, rows_local: int, stream: int = 0):
+        self._check(self.L.moe_tp_allgather(self.h, C.c_void_p(src_ptr), rows_local, C.c_void_p(stream)))
+
+    def tp_reduce_scatter(self, rows_local: int, out_ptr: int, stream: int = 0):
+        self._check(self.L.moe_tp_reduce_scatter(self.h, rows_local, C.c_void_p(out_ptr), C.c_void_p(stream)))
+
     def debug(self, which: int) -> np.ndarray:
         T, E, K, H = self.rows, self.E, self.K, self.H
         shape, dt = {
             DBG_LOGITS: ((T, E), np.float32), DBG_TOPK_IDX: ((T, K), np.int32), DBG_TOPK_W: ((T, K), np.float32),
             DBG_COUNTS: ((E,), np.int32), DBG_OFFSETS: ((E + 1,), np.int32), DBG_PAIR_ROW: ((T, K), np.int32),
             DBG_ROW_TOKEN: ((T * K,), np.int32), DBG_OUT_F32: ((T, H), np.float32),
-            DBG_STATUS: ((1,), np.uint32), DBG_YBUF: ((T * K, H), np.float32)}[which]
+            DBG_STATUS: ((1,), np.uint32), DBG_YBUF: ((T * K, H), np.float32),
+            DBG_GATHER: ((T, H), np.uint16)}[which]
         out = np.empty(shape, dtype=dt)
         self._check(self.L.moe_get_debug(self.h, which, out.ctypes.data_as(C.c_void_p), out.nbytes))
         return out

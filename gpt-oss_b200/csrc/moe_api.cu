@@ -211,6 +211,15 @@ int moe_create(const moe_config *cfg, moe_handle *out) {
   if ((rc = dev_alloc(c, &c->ybuf, P * c->H))) return rc;
   if ((rc = dev_alloc(c, &c->out_f32, T * c->H))) return rc;
   if ((rc = dev_alloc(c, &c->out_bf16, T * c->H))) return rc;
+  // symmetric buffers of the TP group; this rank's own entries are known now
+  if ((rc = dev_alloc(c, &c->tp_partial, T * c->H))) return rc;
+  if ((rc = dev_alloc(c, &c->tp_flags, static_cast<size_t>(2) * kMaxTp))) return rc;
+  CU_TRY(c, cudaMemset(c->tp_flags, 0, 2 * kMaxTp * sizeof(uint32_t)));
+  if (cfg->tp_size > kMaxTp) return fail(c, MOE_ERR_INVALID, "tp_size %d above %d", cfg->tp_size, kMaxTp);
+  c->peers.gather[cfg->tp_rank] = c->t_in;
+  c->peers.partial[cfg->tp_rank] = c->tp_partial;
+  c->peers.flags[cfg->tp_rank] = c->tp_flags;
+  c->tp_attached |= 7u << (3 * cfg->tp_rank);
   const int n_nt1 = (c->R1 + kTileN - 1) / kTileN, n_nt2 = (c->H + kTileN - 1) / kTileN;
   c->max_tiles = c->max_pairs / kTokTile + c->E + 1;
   c->max_work1 = c->max_tiles * n_nt1;
@@ -255,6 +264,8 @@ int moe_destroy(moe_handle c) {
   if (!c) return MOE_ERR_INVALID;
   cudaSetDevice(c->cfg.device);
   if (c->stream) { cudaStreamSynchronize(c->stream); cudaStreamDestroy(c->stream); }
+  for (void *p : c->ipc_opened) cudaIpcCloseMemHandle(p);
+  cudaFree(c->tp_partial); cudaFree(c->tp_flags);
   for (auto &w : c->layers) free_layer(w);
   for (cudaEvent_t e : c->prof_events) cudaEventDestroy(e);
   for (cudaEvent_t e : c->prof_pool) cudaEventDestroy(e);
@@ -515,6 +526,7 @@ int moe_get_debug(moe_handle c, int which, void *dst, size_t bytes) {
     case MOE_DBG_ROW_TOKEN: src = c->row_token; have = T * c->K * 4; break;
     case MOE_DBG_OUT_F32: src = c->out_f32; have = T * c->H * 4; break;
     case MOE_DBG_STATUS: src = c->status; have = 4096 * 4; break;
+    case MOE_DBG_GATHER: src = c->t_in; have = T * c->H * 2; break;
     case MOE_DBG_YBUF: src = c->ybuf; have = T * c->K * c->H * 4; break;
     default: return fail(c, MOE_ERR_INVALID, "moe_get_debug: unknown item %d", which);
   }

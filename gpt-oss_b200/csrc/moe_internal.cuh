@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <algorithm>
 #include <string>
 #include <vector>
 
@@ -32,6 +33,15 @@ enum : unsigned {
   ST_WAIT_DEMPTY = 32u,   // expert GEMM: accumulator never drained
   ST_BAD_INDEX = 64u,     // routing produced an out-of-range row
   ST_WAIT_PEER = 128u,    // TP collective: a peer's flag never arrived
+};
+
+constexpr int kMaxTp = 8;  // MAX_TP of getp-csrc/nccl.hpp:6
+// Symmetric buffers of a tensor-parallel group as seen from one rank: entry r is rank r's buffer
+// (a peer mapping, or this rank's own memory for r == rank).
+struct TpPeers {
+  void *gather[kMaxTp];       // bf16 [max_rows, H]: all-gather destination (gather_x_g)
+  void *partial[kMaxTp];      // bf16 [max_rows, H]: this rank's partial block output (e_agg_g)
+  uint32_t *flags[kMaxTp];    // [2 phases][kMaxTp] epoch words
 };
 
 // One work item of the grouped GEMM.
@@ -122,6 +132,12 @@ struct moe_ctx {
   CUtensorMap tm_x1, tm_x2;
   int last_rows = 0;
   long long launches = 0;
+  moe::TpPeers peers = {};          // TP group view; own entries are set at creation
+  __nv_bfloat16 *tp_partial = nullptr;  // this rank's bf16 partial output [max_rows, H]
+  uint32_t *tp_flags = nullptr;     // [2][kMaxTp], written by the peers
+  unsigned tp_attached = 0;         // bit (3*r + which) set once rank r's buffer `which` is known
+  uint32_t tp_epoch = 0, tp_epoch_rs = 0;  // all-gather / reduce-scatter call counters
+  std::vector<void *> ipc_opened;   // mappings to close at destroy
   bool profiling = false;
   std::vector<cudaEvent_t> prof_events;  // MOE_N_STAGES + 1 per profiled call
   std::vector<cudaEvent_t> prof_pool;    // recycled events
@@ -153,6 +169,14 @@ void launch_expert_gemm_mlp1(const CUtensorMap &tm_w, const CUtensorMap &tm_x, c
                              cudaStream_t s);
 void launch_expert_gemm_mlp2(const CUtensorMap &tm_w, const CUtensorMap &tm_x, const GemmArgs &a, int grid,
                              cudaStream_t s);
+
+// tp_collectives.cu
+void launch_tp_allgather_push(const __nv_bfloat16 *src, int rows_local, int H, const TpPeers &peers, int tp, int rank,
+                              int sm_count, cudaStream_t s);
+void launch_tp_signal_wait(const TpPeers &peers, uint32_t *my_flags, int tp, int rank, int phase, uint32_t epoch,
+                           unsigned int *status, cudaStream_t s);
+void launch_tp_reduce_scatter_pull(const TpPeers &peers, int tp, int rank, int rows_local, int H, __nv_bfloat16 *out,
+                                   int sm_count, cudaStream_t s);
 
 // expert_gemm_simt.cu (validation path)
 void launch_simt_mlp1(const uint8_t *codes, int pitch, const uint8_t *scales_raw, const __nv_bfloat16 *bias,

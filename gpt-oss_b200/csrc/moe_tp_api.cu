@@ -1,0 +1,150 @@
+// Host side of the tensor-parallel entry points of include/moe_b200.h: symmetric buffer
+// exchange (replaces tp_init / tp_enable_p2p, getp-csrc/nccl.hpp:41-98) and the launch
+// sequence all-gather -> block -> reduce-scatter (moe_gpu_120b, getp_run.cpp:2958-3246).
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "moe_internal.cuh"
+
+using namespace moe;
+
+namespace {
+
+int tp_fail(moe_ctx *c, int code, const char *fmt, ...) {
+  char buf[400];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  c->err = buf;
+  return code;
+}
+
+void **slot(moe_ctx *c, int which, int rank) {
+  switch (which) {
+    case MOE_TP_BUF_GATHER: return &c->peers.gather[rank];
+    case MOE_TP_BUF_PARTIAL: return &c->peers.partial[rank];
+    case MOE_TP_BUF_FLAGS: return reinterpret_cast<void **>(&c->peers.flags[rank]);
+    default: return nullptr;
+  }
+}
+
+bool group_complete(const moe_ctx *c) {
+  for (int r = 0; r < c->cfg.tp_size; ++r)
+    for (int w = 0; w < 3; ++w)
+      if (!(c->tp_attached & (1u << (3 * r + w)))) return false;
+  return true;
+}
+
+int check_tp_call(moe_ctx *c, int rows_local, const char *who) {
+  if (c->cfg.tp_size > 1 && !group_complete(c))
+    return tp_fail(c, MOE_ERR_STATE, "%s: not every peer buffer of the %d-rank group is attached", who, c->cfg.tp_size);
+  if (rows_local <= 0 || static_cast<long long>(rows_local) * c->cfg.tp_size > c->max_rows)
+    return tp_fail(c, MOE_ERR_INVALID, "%s: rows_local %d x tp %d exceeds max_rows %d", who, rows_local, c->cfg.tp_size,
+                   c->max_rows);
+  if (cudaSetDevice(c->cfg.device) != cudaSuccess) return tp_fail(c, MOE_ERR_CUDA, "%s: cudaSetDevice failed", who);
+  return MOE_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int moe_tp_buffer(moe_handle c, int which, void **dev_ptr) {
+  if (!c || !dev_ptr) return MOE_ERR_INVALID;
+  void **s = slot(c, which, c->cfg.tp_rank);
+  if (!s) return tp_fail(c, MOE_ERR_INVALID, "moe_tp_buffer: unknown buffer %d", which);
+  *dev_ptr = *s;
+  return MOE_OK;
+}
+
+int moe_tp_export(moe_handle c, int which, void *handle_out) {
+  if (!c || !handle_out) return MOE_ERR_INVALID;
+  void **s = slot(c, which, c->cfg.tp_rank);
+  if (!s) return tp_fail(c, MOE_ERR_INVALID, "moe_tp_export: unknown buffer %d", which);
+  if (cudaSetDevice(c->cfg.device) != cudaSuccess) return tp_fail(c, MOE_ERR_CUDA, "moe_tp_export: cudaSetDevice failed");
+  static_assert(sizeof(cudaIpcMemHandle_t) == MOE_TP_HANDLE_BYTES, "handle size");
+  cudaError_t e = cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t *>(handle_out), *s);
+  if (e != cudaSuccess) return tp_fail(c, MOE_ERR_CUDA, "cudaIpcGetMemHandle: %s", cudaGetErrorString(e));
+  return MOE_OK;
+}
+
+int moe_tp_attach_ipc(moe_handle c, int which, int rank, const void *handle_in) {
+  if (!c || !handle_in) return MOE_ERR_INVALID;
+  if (rank < 0 || rank >= c->cfg.tp_size || !slot(c, which, 0))
+    return tp_fail(c, MOE_ERR_INVALID, "moe_tp_attach_ipc: rank %d / buffer %d out of range", rank, which);
+  if (rank == c->cfg.tp_rank) return MOE_OK;  // own buffers are known since creation
+  if (cudaSetDevice(c->cfg.device) != cudaSuccess) return tp_fail(c, MOE_ERR_CUDA, "moe_tp_attach_ipc: cudaSetDevice failed");
+  void *p = nullptr;
+  cudaIpcMemHandle_t hd;
+  memcpy(&hd, handle_in, sizeof(hd));
+  cudaError_t e = cudaIpcOpenMemHandle(&p, hd, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return tp_fail(c, MOE_ERR_CUDA, "cudaIpcOpenMemHandle(rank %d): %s", rank, cudaGetErrorString(e));
+  c->ipc_opened.push_back(p);
+  *slot(c, which, rank) = p;
+  c->tp_attached |= 1u << (3 * rank + which);
+  return MOE_OK;
+}
+
+int moe_tp_attach_ptr(moe_handle c, int which, int rank, void *dev_ptr, int peer_device) {
+  if (!c || !dev_ptr) return MOE_ERR_INVALID;
+  if (rank < 0 || rank >= c->cfg.tp_size || !slot(c, which, 0))
+    return tp_fail(c, MOE_ERR_INVALID, "moe_tp_attach_ptr: rank %d / buffer %d out of range", rank, which);
+  if (rank == c->cfg.tp_rank) return MOE_OK;
+  if (cudaSetDevice(c->cfg.device) != cudaSuccess) return tp_fail(c, MOE_ERR_CUDA, "moe_tp_attach_ptr: cudaSetDevice failed");
+  if (peer_device != c->cfg.device) {
+    int can = 0;
+    cudaDeviceCanAccessPeer(&can, c->cfg.device, peer_device);
+    if (!can) return tp_fail(c, MOE_ERR_CUDA, "device %d cannot access device %d", c->cfg.device, peer_device);
+    cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+    if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled)
+      return tp_fail(c, MOE_ERR_CUDA, "cudaDeviceEnablePeerAccess(%d): %s", peer_device, cudaGetErrorString(e));
+    cudaGetLastError();
+  }
+  *slot(c, which, rank) = dev_ptr;
+  c->tp_attached |= 1u << (3 * rank + which);
+  return MOE_OK;
+}
+
+int moe_tp_allgather(moe_handle c, const void *src, int rows_local, void *stream) {
+  if (!c || !src) return MOE_ERR_INVALID;
+  int rc = check_tp_call(c, rows_local, "moe_tp_allgather");
+  if (rc != MOE_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int tp = c->cfg.tp_size, rank = c->cfg.tp_rank;
+  ++c->tp_epoch;
+  launch_tp_allgather_push(static_cast<const __nv_bfloat16 *>(src), rows_local, c->H, c->peers, tp, rank, c->sm_count, s);
+  launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, 0, c->tp_epoch, c->status, s);
+  c->launches += 2;
+  if (cudaGetLastError() != cudaSuccess) return tp_fail(c, MOE_ERR_CUDA, "moe_tp_allgather: launch failed");
+  return MOE_OK;
+}
+
+int moe_tp_reduce_scatter(moe_handle c, int rows_local, void *out_local, void *stream) {
+  if (!c || !out_local) return MOE_ERR_INVALID;
+  int rc = check_tp_call(c, rows_local, "moe_tp_reduce_scatter");
+  if (rc != MOE_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int tp = c->cfg.tp_size, rank = c->cfg.tp_rank;
+  ++c->tp_epoch_rs;  // every rank calls in lock-step, so the counters agree across the group
+  launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, 1, c->tp_epoch_rs, c->status, s);
+  launch_tp_reduce_scatter_pull(c->peers, tp, rank, rows_local, c->H, static_cast<__nv_bfloat16 *>(out_local),
+                                c->sm_count, s);
+  c->launches += 2;
+  if (cudaGetLastError() != cudaSuccess) return tp_fail(c, MOE_ERR_CUDA, "moe_tp_reduce_scatter: launch failed");
+  return MOE_OK;
+}
+
+int moe_tp_forward(moe_handle c, int layer, const void *t_local, int rows_local, void *out_local, unsigned flags,
+                   void *stream) {
+  if (!c || !t_local || !out_local) return MOE_ERR_INVALID;
+  int rc = moe_tp_allgather(c, t_local, rows_local, stream);
+  if (rc != MOE_OK) return rc;
+  const int T = rows_local * c->cfg.tp_size;
+  rc = moe_forward(c, layer, c->peers.gather[c->cfg.tp_rank], T, c->tp_partial, flags & ~MOE_FWD_PARTIAL_F32, stream);
+  if (rc != MOE_OK) return rc;
+  return moe_tp_reduce_scatter(c, rows_local, out_local, stream);
+}
+
+}  // extern "C"

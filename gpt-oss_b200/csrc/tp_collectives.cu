@@ -1,0 +1,112 @@
+// Tensor-parallel exchange of the MoE block over NVLink peer memory.
+//
+// Reference counterparts: ring_allgather_rows_bf16 (getp-csrc/tp_ring.hpp:70-118)
+// or the direct pulls of moe_gpu (getp_run.cpp:2580-2607) before the MLPs; the
+// pull-and-add reduce-scatter of moe_gpu_120b (getp_run.cpp:3206-3246, with
+// vec_add_inplace_bf16, tp_ring.hpp:220-231) after them; and the host spin
+// barrier tp_group_barrier (getp-csrc/nccl.hpp:116-137).  The reference drives
+// hipMemcpyPeerAsync from the host and synchronises stream and host between
+// ring steps.  Behind NVSwitch every peer is one hop away, so a ring buys
+// nothing: each rank PUSHES its rows into every peer's gather buffer with plain
+// 16-byte stores, and each row owner PULLS its slice of every peer's partial
+// output and adds them in rank order (fp32 add, bf16 payloads, deterministic).
+// The host barrier becomes per-peer epoch flags in device memory, written with
+// st.release.sys and polled with a bounded ld.acquire.sys loop.
+//
+// Kernels of different ranks wait on one another, so every rank of a group must
+// run on its own GPU.  No TMA, no multicast: ordinary loads/stores on peer
+// pointers.
+#include "moe_internal.cuh"
+
+namespace moe {
+
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Every rank's rows [rows_local, H] -> slot `rank` of the gather buffer of every rank of the group.
+__global__ void __launch_bounds__(256)
+tp_allgather_push_kernel(const uint4 *__restrict__ src, size_t n_vec, TpPeers peers, int tp, size_t slot_vec) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
+    const uint4 v = __ldg(src + i);
+    for (int r = 0; r < tp; ++r) reinterpret_cast<uint4 *>(peers.gather[r])[slot_vec + i] = v;
+  }
+}
+
+// Tells every peer "my data of this phase and epoch is in place" and waits until every peer has said
+// the same.  flags layout on each rank: [phase][tp] words, word [phase][r] written by rank r.
+// One warp; lane r handles peer r.  The wait is bounded (about a second).
+__global__ void tp_signal_wait_kernel(TpPeers peers, uint32_t *my_flags, int tp, int rank, int phase, uint32_t epoch,
+                                      unsigned int *status) {
+  const int r = threadIdx.x;
+  __threadfence_system();
+  if (r < tp) st_release_sys(peers.flags[r] + phase * kMaxTp + rank, epoch);
+  if (r < tp) {
+    const uint32_t *f = my_flags + phase * kMaxTp + r;
+    const long long t0 = clock64();
+    bool ok = false;
+    for (uint32_t spin = 0;; ++spin) {
+      // epochs only grow; signed difference tolerates wrap-around
+      if (static_cast<int32_t>(ld_acquire_sys(f) - epoch) >= 0) { ok = true; break; }
+      if ((spin & 255u) == 255u && clock64() - t0 > 2000000000LL) break;
+    }
+    if (!ok) atomicOr(status, ST_WAIT_PEER);
+  }
+  __threadfence_system();
+}
+
+// out[i] = bf16( sum over ranks r = 0..tp-1 of peer_partial[r][slot + i] ), fp32 adds in rank order.
+__global__ void __launch_bounds__(256)
+tp_reduce_scatter_pull_kernel(TpPeers peers, int tp, size_t slot_vec, size_t n_vec, uint4 *__restrict__ out) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int r = 0; r < tp; ++r) {
+      const uint4 v = reinterpret_cast<const uint4 *>(peers.partial[r])[slot_vec + i];
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[2 * j] += __uint_as_float(w[j] << 16);
+        acc[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u);
+      }
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __nv_bfloat162 b = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+      o[j] = *reinterpret_cast<const uint32_t *>(&b);
+    }
+    out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+void launch_tp_allgather_push(const __nv_bfloat16 *src, int rows_local, int H, const TpPeers &peers, int tp, int rank,
+                              int sm_count, cudaStream_t s) {
+  const size_t n_vec = static_cast<size_t>(rows_local) * H / 8;
+  const int blocks = static_cast<int>(std::min<size_t>((n_vec + 255) / 256, static_cast<size_t>(sm_count) * 4));
+  tp_allgather_push_kernel<<<std::max(blocks, 1), 256, 0, s>>>(reinterpret_cast<const uint4 *>(src), n_vec, peers, tp,
+                                                              static_cast<size_t>(rank) * n_vec);
+}
+
+void launch_tp_signal_wait(const TpPeers &peers, uint32_t *my_flags, int tp, int rank, int phase, uint32_t epoch,
+                           unsigned int *status, cudaStream_t s) {
+  tp_signal_wait_kernel<<<1, 32, 0, s>>>(peers, my_flags, tp, rank, phase, epoch, status);
+}
+
+void launch_tp_reduce_scatter_pull(const TpPeers &peers, int tp, int rank, int rows_local, int H, __nv_bfloat16 *out,
+                                   int sm_count, cudaStream_t s) {
+  const size_t n_vec = static_cast<size_t>(rows_local) * H / 8;
+  const int blocks = static_cast<int>(std::min<size_t>((n_vec + 255) / 256, static_cast<size_t>(sm_count) * 4));
+  tp_reduce_scatter_pull_kernel<<<std::max(blocks, 1), 256, 0, s>>>(peers, tp, static_cast<size_t>(rank) * n_vec, n_vec,
+                                                                    reinterpret_cast<uint4 *>(out));
+}
+
+}  // namespace moe

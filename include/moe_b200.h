@@ -106,6 +106,36 @@ void moe_host_free(void *p);
  * pointers).  Replaces run_route_select_softmax_fused (kernels/moe.hpp:565-599). */
 int moe_route_topk(moe_handle h, const float *logits_dev, int rows, int *idx_dev, float *w_dev, void *stream);
 
+/* ---- tensor-parallel group (replaces TPGroup / tp_init / tp_enable_p2p, getp-csrc/nccl.hpp:25-98, and
+ * the raw peer pointers the reference reads through gpu_transformers[], getp_run.cpp:2594,:2965,:3221).
+ * A handle created with tp_size > 1 owns three symmetric buffers; every rank must learn every peer's. */
+enum {
+  MOE_TP_BUF_GATHER = 0,  /* bf16 [max_rows, H]  all-gather destination        (gather_x_g) */
+  MOE_TP_BUF_PARTIAL = 1, /* bf16 [max_rows, H]  this rank's partial output    (e_agg_g)    */
+  MOE_TP_BUF_FLAGS = 2    /* u32  [2][8]         arrival epochs written by the peers        */
+};
+#define MOE_TP_HANDLE_BYTES 64 /* sizeof(cudaIpcMemHandle_t) */
+/* Ranks in different processes: export, exchange the 64 bytes by any channel, attach. */
+int moe_tp_export(moe_handle h, int which, void *handle_out);
+int moe_tp_attach_ipc(moe_handle h, int which, int rank, const void *handle_in);
+/* Ranks in one process (one host thread per GPU, as the reference runs): pass the raw pointer. */
+int moe_tp_buffer(moe_handle h, int which, void **dev_ptr);
+int moe_tp_attach_ptr(moe_handle h, int which, int rank, void *dev_ptr, int peer_device);
+
+/* Replaces moe_gpu_120b steps 1-9 (getp_run.cpp:2958-3246): all-gather of every rank's `rows_local`
+ * normalised bf16 rows, the block on the union of tp_size * rows_local rows with this rank's weight
+ * shard, and the reduce-scatter that leaves the summed bf16 rows of THIS rank in out_local_dev.
+ * Every rank of the group must call it with the same rows_local; each rank runs on its own GPU.
+ * Device-side waits on peers are bounded; a wait that ran out shows as MOE_ERR_TIMEOUT from
+ * moe_synchronize().  Stream-ordered, no host synchronisation (the reference synchronises stream and
+ * host threads between steps, getp_run.cpp:2955-2956,:3203-3204). */
+int moe_tp_forward(moe_handle h, int layer, const void *t_local_dev, int rows_local, void *out_local_dev,
+                   unsigned flags, void *stream);
+/* The two collectives alone: ring_allgather_rows_bf16 (tp_ring.hpp:70-118) into the gather buffer, and
+ * the owner-slice reduce-scatter (getp_run.cpp:3206-3246) of the partial buffers into out_local_dev. */
+int moe_tp_allgather(moe_handle h, const void *src_local_dev, int rows_local, void *stream);
+int moe_tp_reduce_scatter(moe_handle h, int rows_local, void *out_local_dev, void *stream);
+
 /* No counterpart in the reference.  Router + top-k + softmax for a caller that must not reach
  * the CUDA allocator when it needs a routing decision (its memory was handed out once by a pool
  * that owns the device, or it cannot afford the device-wide synchronisation inside cudaMalloc).
@@ -130,7 +160,8 @@ enum {
   MOE_DBG_ROW_TOKEN = 6,/* i32 [rows*K]     expert_row_token_g */
   MOE_DBG_OUT_F32 = 7,  /* f32 [rows, H]    block output before the bf16 rounding (MOE_CFG_KEEP_F32_OUT) */
   MOE_DBG_STATUS = 8,   /* u32 [4096]       device status word (first element) and diagnostics */
-  MOE_DBG_YBUF = 10     /* f32 [rows*K, H]  MLP2 output, permuted rows (expert_output_partial_g) */
+  MOE_DBG_YBUF = 10,    /* f32 [rows*K, H]  MLP2 output, permuted rows (expert_output_partial_g) */
+  MOE_DBG_GATHER = 11   /* bf16 [rows, H]   all-gather destination of the TP group (gather_x_g) */
 };
 int moe_get_debug(moe_handle h, int which, void *host_dst, size_t bytes);
 
