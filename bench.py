@@ -45,12 +45,20 @@ CPU_SAMPLE_TOKENS = 32
 NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.015
 
 
-def workload_config(tokens: int, n_gpus: int) -> dict:
+def workload_config(tokens: int, n_gpus: int, parallel: str = "tp") -> dict:
+    if n_gpus == 1:
+        par = "tp1"
+    elif parallel == "tp":
+        par = (f"tp{n_gpus}: intermediate dimension sharded over {n_gpus} GPUs, every rank owns {tokens} rows, the "
+               f"block runs on the union of {n_gpus * tokens} rows; all-gather before and reduce-scatter after by "
+               f"peer-memory kernels over NVLink")
+    else:
+        par = f"tp1 x dp{n_gpus} (independent replicas, no collective)"
     return {
         "workload": f"GPT-OSS-120B-shape MoE layer (E=128, top-4, hidden 2880, intermediate 2880, MXFP4 "
                     f"weights, E8M0 scales), {tokens} bf16 rows per GPU, seed 0",
         "rows_per_gpu": tokens,
-        "parallelism": "tp1" if n_gpus == 1 else f"tp1 x dp{n_gpus} (independent replicas)",
+        "parallelism": par,
         "l2_policy": "inputs larger than L2: 1.69 GB of expert weights are streamed every step (L2 is 126 MB)",
     }
 
@@ -144,6 +152,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=1856)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--parallel", default="tp", choices=["tp", "dp"],
+                    help="at N > 1: one tensor-parallel group of N ranks (default) or N independent replicas")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -153,7 +163,7 @@ def main():
     synth = pkg.synth
     E, H, D, K = SHAPE["E"], SHAPE["H"], SHAPE["D"], SHAPE["K"]
     T = args.tokens
-    cfg = workload_config(T, args.gpus)
+    cfg = workload_config(T, args.gpus, args.parallel)
 
     if args.impl == "reference":
         if rank != 0:
@@ -191,17 +201,27 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    tp = world if (world > 1 and args.parallel == "tp") else 1
     layer = synth.make_layer(E, H, D, seed=0)
     tokens = synth.make_tokens(T, H, seed=rank)
-    blk = pkg.MoeBlock(H, D, E, top_k=K, max_rows=T, device=local_rank)
+    blk = pkg.MoeBlock(H, D, E, top_k=K, max_rows=T * tp, tp_size=tp, tp_rank=rank if tp > 1 else 0,
+                       device=local_rank)
     blk.load_layer(0, layer)
+    if tp > 1:
+        tpmod = importlib.import_module("gpt-oss_b200.tp")
+        tpmod.attach_group(blk, rank, dist.new_group(backend="gloo"))
+    Dl = blk.Dl
+    Tu = T * tp                      # rows the block sees on every rank
     d_t = torch.from_numpy(tokens.view(np.int16)).cuda()
     d_o = torch.empty_like(d_t)
     stream = torch.cuda.current_stream()
     sp = stream.cuda_stream
 
     def step():
-        blk.forward(0, d_t.data_ptr(), T, d_o.data_ptr(), 0, sp)
+        if tp > 1:
+            blk.tp_forward(0, d_t.data_ptr(), T, d_o.data_ptr(), 0, sp)
+        else:
+            blk.forward(0, d_t.data_ptr(), T, d_o.data_ptr(), 0, sp)
 
     for _ in range(warmup):
         step()
@@ -241,14 +261,51 @@ def main():
     pin_in = pkg.PinnedBuffer((T, H), np.uint16)
     pin_out = pkg.PinnedBuffer((T, H), np.uint16)
     pin_in.array[:] = tokens
+    def host_step():
+        if tp > 1:
+            blk.tp_forward_host(0, pin_in.array, pin_out.array)
+        else:
+            blk.forward_host(0, pin_in.array, out=pin_out.array)
+
     for _ in range(3):
-        blk.forward_host(0, pin_in.array, out=pin_out.array)
+        host_step()
     barrier(); torch.cuda.synchronize()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        blk.forward_host(0, pin_in.array, out=pin_out.array)
+        host_step()
     e2e_s = max_over_ranks(time.perf_counter() - t0)
     barrier()
+
+    # ---- D (TP only): the two collectives alone, this library's peer-memory kernels vs NCCL ----
+    coll = None
+    if tp > 1:
+        def timed(fn, n):
+            for _ in range(3):
+                fn()
+            barrier(); torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            for _ in range(n):
+                fn()
+            b.record(stream)
+            torch.cuda.synchronize(); barrier()
+            return max_over_ranks(a.elapsed_time(b)) / n
+        n = min(args.steps, 50)
+        bt = d_t.view(torch.bfloat16)
+        g_full = torch.empty((Tu, H), dtype=torch.bfloat16, device="cuda")
+        g_part = torch.randn((Tu, H), dtype=torch.float32, device="cuda").to(torch.bfloat16)
+        g_out = torch.empty((T, H), dtype=torch.bfloat16, device="cuda")
+        ours_ag = timed(lambda: blk.tp_allgather(d_t.data_ptr(), T, sp), n)
+        ours_rs = timed(lambda: blk.tp_reduce_scatter(T, d_o.data_ptr(), sp), n)
+        nccl_ag = timed(lambda: dist.all_gather_into_tensor(g_full, bt), n)
+        nccl_rs = timed(lambda: dist.reduce_scatter_tensor(g_out, g_part), n)
+        per_dir = (tp - 1) / tp * Tu * H * 2     # bytes each rank sends (and receives) per collective
+        coll = {"rows_per_rank": T, "bytes_per_rank_per_direction": per_dir,
+                "allgather_ms": {"ours": ours_ag, "nccl": nccl_ag},
+                "reduce_scatter_ms": {"ours": ours_rs, "nccl": nccl_rs},
+                "allgather_gbs_per_direction": {"ours": per_dir / ours_ag / 1e6, "nccl": per_dir / nccl_ag / 1e6},
+                "reduce_scatter_gbs_per_direction": {"ours": per_dir / ours_rs / 1e6, "nccl": per_dir / nccl_rs / 1e6},
+                "nvlink_peer_copy_measured_gbs": 770.0}
     loss_like = float(synth.bf16_bits_to_f32(pin_out.array[:4]).sum())  # the result was read back
     clocks = sampler.stop() if sampler else None
 
@@ -260,13 +317,16 @@ def main():
     hbm_peak, tc_peak, peak_kind = peaks()
     ms_step = ms_total / args.steps
     value = world * T / (ms_step * 1e-3)
-    P = T * K
-    R1 = 2 * D
-    mlp1_bytes = active * (R1 * H // 2 + R1 * H // 32 + R1 * 2) + P * H * 2 + P * D * 2
+    P = Tu * K
+    R1 = 2 * Dl                      # this rank's MLP1 rows per expert
+    mlp1_bytes = active * (R1 * H // 2 + R1 * H // 32 + R1 * 2) + P * H * 2 + P * Dl * 2
     mlp1_flops = 2.0 * P * R1 * H
     mlp1_s = stage_ms["mlp1"] / max(ncalls, 1) * 1e-3
     achieved = mlp1_bytes / mlp1_s / 1e9
-    flops, nbytes = synth.algorithmic_work(T, H, D, E, K, active)
+    flops, nbytes = synth.algorithmic_work(Tu, H, D, E, K, active)
+    if tp > 1:                       # per rank: 1/tp of the expert weights and flops, all of the rows
+        flops = (flops - Tu * 2 * H * E) / tp + Tu * 2 * H * E
+        nbytes = active * synth.weight_bytes_per_expert(H, D) / tp + Tu * H * 2 * 2 + E * H * 4
     out = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
@@ -290,6 +350,10 @@ def main():
         "stage_ms": {k: v / max(ncalls, 1) for k, v in stage_ms.items()},
         "checksum": loss_like,
     }
+    if coll is not None:
+        out["collectives"] = coll
+        out["stage_ms"]["allgather+reduce_scatter (step minus block stages)"] = \
+            ms_step - sum(v / max(ncalls, 1) for v in stage_ms.values())
     if args.gpus == 1 and not args.no_cpu_baseline:
         sample = tokens[:CPU_SAMPLE_TOKENS]
         tps, kind, cores, _ = cpu_reference_arm(layer, sample, 2, 1)

@@ -34,7 +34,7 @@ EXPORTS = [
     "moe_synchronize", "moe_host_alloc", "moe_host_free", "moe_route_topk", "moe_get_debug",
     "moe_last_error", "moe_strerror", "moe_launch_count", "moe_profile_enable", "moe_profile_collect",
     "moe_route_static", "moe_tp_export", "moe_tp_attach_ipc", "moe_tp_buffer", "moe_tp_attach_ptr",
-    "moe_tp_forward", "moe_tp_allgather", "moe_tp_reduce_scatter",
+    "moe_tp_forward", "moe_tp_forward_host", "moe_tp_allgather", "moe_tp_reduce_scatter",
 ]
 TP_BUF_GATHER, TP_BUF_PARTIAL, TP_BUF_FLAGS = 0, 1, 2
 TP_HANDLE_BYTES = 64
@@ -90,6 +90,7 @@ def lib() -> C.CDLL:
         L.moe_tp_buffer.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_void_p)]
         L.moe_tp_attach_ptr.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int]
         L.moe_tp_forward.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_uint, C.c_void_p]
+        L.moe_tp_forward_host.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_uint]
         L.moe_tp_allgather.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
         L.moe_tp_reduce_scatter.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
         L.moe_profile_enable.argtypes = [C.c_void_p, C.c_int]
@@ -219,6 +220,13 @@ class MoeBlock:
         self._check(self.L.moe_tp_forward(self.h, layer, C.c_void_p(t_ptr), rows_local, C.c_void_p(out_ptr), flags,
                                           C.c_void_p(stream)))
         self.rows = rows_local * self.cfg.tp_size
+
+    def tp_forward_host(self, layer: int, t_bits: np.ndarray, out: np.ndarray, flags: int = 0) -> np.ndarray:
+        rows = t_bits.shape[0]
+        self._check(self.L.moe_tp_forward_host(self.h, layer, t_bits.ctypes.data_as(C.c_void_p), rows,
+                                               out.ctypes.data_as(C.c_void_p), flags))
+        self.rows = rows * self.cfg.tp_size
+        return out
 
     def tp_allgather(self, src_ptr: int, rows_local: int, stream: int = 0):
         self._check(self.L.moe_tp_allgather(self.h, C.c_void_p(src_ptr), rows_local, C.c_void_p(stream)))

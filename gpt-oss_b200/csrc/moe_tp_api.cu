@@ -147,4 +147,29 @@ int moe_tp_forward(moe_handle c, int layer, const void *t_local, int rows_local,
   return moe_tp_reduce_scatter(c, rows_local, out_local, stream);
 }
 
+int moe_tp_forward_host(moe_handle c, int layer, const void *t_local_host, int rows_local, void *out_local_host,
+                        unsigned flags) {
+  if (!c || !t_local_host || !out_local_host) return MOE_ERR_INVALID;
+  int rc = check_tp_call(c, rows_local, "moe_tp_forward_host");
+  if (rc != MOE_OK) return rc;
+  const size_t bytes = static_cast<size_t>(rows_local) * c->H * 2;
+  // staging: the fp32 debug buffer is unused on this path and large enough ([max_rows, H] fp32)
+  __nv_bfloat16 *in_dev = reinterpret_cast<__nv_bfloat16 *>(c->out_f32);
+  __nv_bfloat16 *out_dev = c->out_bf16;
+  if (cudaMemcpyAsync(in_dev, t_local_host, bytes, cudaMemcpyHostToDevice, c->stream) != cudaSuccess)
+    return tp_fail(c, MOE_ERR_CUDA, "moe_tp_forward_host: host-to-device copy failed");
+  rc = moe_tp_forward(c, layer, in_dev, rows_local, out_dev, flags & ~MOE_FWD_PARTIAL_F32, c->stream);
+  if (rc != MOE_OK) return rc;
+  if (cudaMemcpyAsync(out_local_host, out_dev, bytes, cudaMemcpyDeviceToHost, c->stream) != cudaSuccess ||
+      cudaStreamSynchronize(c->stream) != cudaSuccess)
+    return tp_fail(c, MOE_ERR_CUDA, "moe_tp_forward_host: device-to-host copy failed: %s", cudaGetErrorString(cudaGetLastError()));
+  unsigned st = 0;
+  cudaMemcpy(&st, c->status, sizeof(st), cudaMemcpyDeviceToHost);
+  if (st) {
+    cudaMemset(c->status, 0, sizeof(unsigned));
+    return tp_fail(c, (st & ST_BAD_INDEX) ? MOE_ERR_STATE : MOE_ERR_TIMEOUT, "device status word 0x%x", st);
+  }
+  return MOE_OK;
+}
+
 }  // extern "C"

@@ -131,6 +131,9 @@ int moe_tp_attach_ptr(moe_handle h, int which, int rank, void *dev_ptr, int peer
  * host threads between steps, getp_run.cpp:2955-2956,:3203-3204). */
 int moe_tp_forward(moe_handle h, int layer, const void *t_local_dev, int rows_local, void *out_local_dev,
                    unsigned flags, void *stream);
+/* moe_tp_forward for HOST buffers of this rank's rows (copies inside, waits, returns the device status). */
+int moe_tp_forward_host(moe_handle h, int layer, const void *t_local_host, int rows_local, void *out_local_host,
+                        unsigned flags);
 /* The two collectives alone: ring_allgather_rows_bf16 (tp_ring.hpp:70-118) into the gather buffer, and
  * the owner-slice reduce-scatter (getp_run.cpp:3206-3246) of the partial buffers into out_local_dev. */
 int moe_tp_allgather(moe_handle h, const void *src_local_dev, int rows_local, void *stream);
