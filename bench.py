@@ -45,13 +45,24 @@ CPU_SAMPLE_TOKENS = 32
 NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.015
 
 
-def workload_config(tokens: int, n_gpus: int, parallel: str = "tp") -> dict:
+def tp_size_for(n_gpus: int, parallel: str, tp_arg: int) -> int:
+    """TP group size at N GPUs: the reference's deployments (TP2 x DP4 for 20B, TP4 x DP2 for 120B,
+    getp-csrc/getp_run.cpp:1850-1853) cap the group at 4; more GPUs add data-parallel replicas of it."""
+    if n_gpus == 1 or parallel == "dp":
+        return 1
+    tp = tp_arg if tp_arg > 0 else min(n_gpus, 4)
+    assert n_gpus % tp == 0
+    return tp
+
+
+def workload_config(tokens: int, n_gpus: int, parallel: str = "tp", tp_arg: int = 0) -> dict:
+    tp = tp_size_for(n_gpus, parallel, tp_arg)
     if n_gpus == 1:
         par = "tp1"
-    elif parallel == "tp":
-        par = (f"tp{n_gpus}: intermediate dimension sharded over {n_gpus} GPUs, every rank owns {tokens} rows, the "
-               f"block runs on the union of {n_gpus * tokens} rows; all-gather before and reduce-scatter after by "
-               f"peer-memory kernels over NVLink")
+    elif tp > 1:
+        par = (f"tp{tp} x dp{n_gpus // tp}: intermediate dimension sharded over {tp} GPUs, every rank owns {tokens} "
+               f"rows, the block runs on the group's union of {tp * tokens} rows; all-gather before and "
+               f"reduce-scatter after by peer-memory kernels over NVLink; groups are independent replicas")
     else:
         par = f"tp1 x dp{n_gpus} (independent replicas, no collective)"
     return {
@@ -153,7 +164,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=1856)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--parallel", default="tp", choices=["tp", "dp"],
-                    help="at N > 1: one tensor-parallel group of N ranks (default) or N independent replicas")
+                    help="at N > 1: tensor-parallel groups (default) or N independent replicas")
+    ap.add_argument("--tp", type=int, default=0, help="TP group size (default min(N, 4))")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -163,7 +175,7 @@ def main():
     synth = pkg.synth
     E, H, D, K = SHAPE["E"], SHAPE["H"], SHAPE["D"], SHAPE["K"]
     T = args.tokens
-    cfg = workload_config(T, args.gpus, args.parallel)
+    cfg = workload_config(T, args.gpus, args.parallel, args.tp)
 
     if args.impl == "reference":
         if rank != 0:
@@ -201,15 +213,20 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    tp = world if (world > 1 and args.parallel == "tp") else 1
+    tp = tp_size_for(world, args.parallel, args.tp)
     layer = synth.make_layer(E, H, D, seed=0)
     tokens = synth.make_tokens(T, H, seed=rank)
-    blk = pkg.MoeBlock(H, D, E, top_k=K, max_rows=T * tp, tp_size=tp, tp_rank=rank if tp > 1 else 0,
-                       device=local_rank)
+    blk = pkg.MoeBlock(H, D, E, top_k=K, max_rows=T * tp, tp_size=tp, tp_rank=rank % tp, device=local_rank)
     blk.load_layer(0, layer)
+    tp_group = None
     if tp > 1:
         tpmod = importlib.import_module("gpt-oss_b200.tp")
-        tpmod.attach_group(blk, rank, dist.new_group(backend="gloo"))
+        for ranks in tpmod.tp_groups(world, tp):          # every rank takes part in creating every group
+            g_gloo = dist.new_group(ranks=ranks, backend="gloo")
+            g_nccl = dist.new_group(ranks=ranks, backend="nccl")
+            if rank in ranks:
+                tp_group = g_nccl
+                tpmod.attach_group(blk, rank % tp, g_gloo)
     Dl = blk.Dl
     Tu = T * tp                      # rows the block sees on every rank
     d_t = torch.from_numpy(tokens.view(np.int16)).cuda()
@@ -297,8 +314,8 @@ def main():
         g_out = torch.empty((T, H), dtype=torch.bfloat16, device="cuda")
         ours_ag = timed(lambda: blk.tp_allgather(d_t.data_ptr(), T, sp), n)
         ours_rs = timed(lambda: blk.tp_reduce_scatter(T, d_o.data_ptr(), sp), n)
-        nccl_ag = timed(lambda: dist.all_gather_into_tensor(g_full, bt), n)
-        nccl_rs = timed(lambda: dist.reduce_scatter_tensor(g_out, g_part), n)
+        nccl_ag = timed(lambda: dist.all_gather_into_tensor(g_full, bt, group=tp_group), n)
+        nccl_rs = timed(lambda: dist.reduce_scatter_tensor(g_out, g_part, group=tp_group), n)
         per_dir = (tp - 1) / tp * Tu * H * 2     # bytes each rank sends (and receives) per collective
         coll = {"rows_per_rank": T, "bytes_per_rank_per_direction": per_dir,
                 "allgather_ms": {"ours": ours_ag, "nccl": nccl_ag},

@@ -25,7 +25,7 @@
 // expanded to the 8-bit containers the MMA reads, 128-byte swizzle), weight
 // scales (two 512-byte atoms, pre-tiled at load time), activations [128 rows x
 // 128] e4m3 (TMA, 128-byte swizzle).  The MMA thread copies the scale atoms to
-// tensor memory (tcgen05.cp) and issues four K = 32 instructions.  Four
+// tensor memory (tcgen05.cp) and issues four K = 32 instructions.  Eight
 // epilogue warps drain the fp32 accumulator (double buffered: 2 x 240 columns).
 // No cluster launch, no multicast: every CTA fetches its own tiles.
 #include <cuda_fp8.h>
@@ -49,9 +49,9 @@ constexpr int kBarOff = kSfaOff + 2 * kSfAtomBytes;
 constexpr int kNumBars = 2 * kStages + 6;         // full, empty, d_full[2], d_empty[2], sfa_full[2]
 constexpr int kSmemBytes = kBarOff + 8 * kNumBars + 16 + 1024 /*alignment slack*/;
 
-constexpr int kEpiWarps = 4;
-constexpr int kProducerWarp = 4, kMmaWarp = 5;
-constexpr int kThreads = 6 * 32;
+constexpr int kEpiWarps = 8;
+constexpr int kProducerWarp = 8, kMmaWarp = 9;
+constexpr int kThreads = 10 * 32;
 
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAccBufCols = kTileN;          // accumulator buffer d at columns d*240
@@ -182,8 +182,10 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     }
   } else {
     // ------------------------------------------------------------- epilogue warps
-    // lane l of warp q holds accumulator row 32q + l: token 16q + l/2, high (even l) or low (odd l) term
-    const int quad = warp;
+    // Warp w reads tensor-memory lanes 32*(w%4).., i.e. accumulator rows 32q + l: token 16q + l/2, high
+    // (even l) or low (odd l) term.  Warps 0-3 take the 16-column chunks 0..7, warps 4-7 chunks 8..14.
+    // Loads are software pipelined: chunk c+1 is in flight while chunk c is processed.
+    const int quad = warp & 3, half = warp >> 2;
     const uint32_t lane_field = static_cast<uint32_t>(quad * 32) << 16;
     const int odd = lane & 1;
     const int tok = quad * 16 + (lane >> 1);
@@ -198,11 +200,12 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       const int n0 = w.ntile * kTileN;
       const bool tok_ok = tok < w.ntok;
       const __nv_bfloat16 *bias_row = p.bias + static_cast<size_t>(w.expert) * p.R;
-      for (int c0 = 0; c0 < kTileN; c0 += 16) {
-        if (n0 + c0 >= p.R) break;  // uniform: rows past the matrix (zero-filled) produce nothing
-        uint32_t v[16];
-        tmem_ld16(tmem_base + lane_field + d * kAccBufCols + c0, v);
-        tmem_wait_ld();
+      const uint32_t acc = tmem_base + lane_field + d * kAccBufCols;
+      // chunks of this warp that hold rows of the matrix (rows past it are zero-filled and produce nothing)
+      const int c_beg = half * 8;
+      const int c_end = min(half ? kTileN / 16 : 8, (p.R - n0 + 15) / 16);
+
+      auto process = [&](const uint32_t (&v)[16], int c0) {
         // sum of the high and low partial products; afterwards even lanes own columns 0-7, odd lanes 8-15
         float tot[8];
 #pragma unroll
@@ -249,6 +252,20 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             dst[1] = make_float4(tot[4] + b[4], tot[5] + b[5], tot[6] + b[6], tot[7] + b[7]);
           }
         }
+      };
+
+      uint32_t va[16], vb[16];
+      int c = c_beg;
+      if (c < c_end) tmem_ld16(acc + c * 16, va);
+      while (c < c_end) {
+        tmem_wait_ld();
+        if (c + 1 < c_end) tmem_ld16(acc + (c + 1) * 16, vb);
+        process(va, c * 16);
+        if (++c >= c_end) break;
+        tmem_wait_ld();
+        if (c + 1 < c_end) tmem_ld16(acc + (c + 1) * 16, va);
+        process(vb, c * 16);
+        ++c;
       }
       tc_fence_before();
       __syncwarp();

@@ -21,7 +21,7 @@ def exchange_blobs(blob: bytes, group=None) -> list[bytes]:
 
 def attach_group(blk, rank: int, group=None) -> None:
     """Exports this rank's buffers, exchanges the handles and attaches every peer's."""
-    blobs = exchange_blobs(blk.tp_export_all(), group)
+    blobs = exchange_blobs(blk.tp_export_all(), group)   # in group-rank order
     for r, b in enumerate(blobs):
         if r != rank:
             blk.tp_attach_all(r, b)
