@@ -369,8 +369,9 @@ def main():
     }
     if coll is not None:
         out["collectives"] = coll
-        out["stage_ms"]["allgather+reduce_scatter (step minus block stages)"] = \
-            ms_step - sum(v / max(ncalls, 1) for v in stage_ms.values())
+        out["stage_notes"] = ("tensor-parallel call: the all-gather push runs beside 'router' on a side stream and its "
+                              "arrival wait is inside 'topk'; the reduce-scatter (peer stores from the combine, arrival "
+                              "wait, slot sum) is inside 'combine'")
     if args.gpus == 1 and not args.no_cpu_baseline:
         sample = tokens[:CPU_SAMPLE_TOKENS]
         tps, kind, cores, _ = cpu_reference_arm(layer, sample, 2, 1)

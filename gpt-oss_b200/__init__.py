@@ -36,7 +36,8 @@ EXPORTS = [
     "moe_route_static", "moe_tp_export", "moe_tp_attach_ipc", "moe_tp_buffer", "moe_tp_attach_ptr",
     "moe_tp_forward", "moe_tp_forward_host", "moe_tp_allgather", "moe_tp_reduce_scatter",
 ]
-TP_BUF_GATHER, TP_BUF_PARTIAL, TP_BUF_FLAGS = 0, 1, 2
+TP_BUF_GATHER, TP_BUF_PARTIAL, TP_BUF_FLAGS, TP_BUF_TOPK_IDX, TP_BUF_TOPK_W = range(5)
+TP_N_BUFS = 5
 TP_HANDLE_BYTES = 64
 STAGES = ("router", "topk", "index", "gather", "mlp1", "mlp2", "combine")
 
@@ -196,18 +197,18 @@ class MoeBlock:
 
     # ---- tensor-parallel group -------------------------------------------------------------
     def tp_export_all(self) -> bytes:
-        """The IPC handles of this rank's three symmetric buffers, 3 x 64 bytes."""
+        """The IPC handles of this rank's symmetric buffers, TP_N_BUFS x 64 bytes."""
         out = b""
-        for which in (TP_BUF_GATHER, TP_BUF_PARTIAL, TP_BUF_FLAGS):
+        for which in range(TP_N_BUFS):
             buf = C.create_string_buffer(TP_HANDLE_BYTES)
             self._check(self.L.moe_tp_export(self.h, which, buf))
             out += buf.raw
         return out
 
     def tp_attach_all(self, rank: int, blob: bytes):
-        """Attaches rank `rank`'s buffers from the 192 bytes its tp_export_all() returned."""
-        assert len(blob) == 3 * TP_HANDLE_BYTES
-        for which in (TP_BUF_GATHER, TP_BUF_PARTIAL, TP_BUF_FLAGS):
+        """Attaches rank `rank`'s buffers from the bytes its tp_export_all() returned."""
+        assert len(blob) == TP_N_BUFS * TP_HANDLE_BYTES
+        for which in range(TP_N_BUFS):
             part = blob[which * TP_HANDLE_BYTES:(which + 1) * TP_HANDLE_BYTES]
             self._check(self.L.moe_tp_attach_ipc(self.h, which, rank, C.c_char_p(part)))
 

@@ -123,8 +123,11 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     if (lane == 0) {
       uint32_t it = 0, item = 0;
       bool ok = true;
+      WorkItem w_next = {};
+      if (static_cast<int>(blockIdx.x) < n_work) w_next = p.work[blockIdx.x];
       for (int wi = blockIdx.x; ok && wi < n_work; wi += gridDim.x, ++item) {
-        const WorkItem w = p.work[wi];
+        const WorkItem w = w_next;
+        if (wi + static_cast<int>(gridDim.x) < n_work) w_next = p.work[wi + gridDim.x];
         // activation scale atom of this token tile; its slot is free once the MMAs of item-2 are done,
         // which the accumulator hand-over of that item (d_empty) has already implied
         const uint32_t d = item & 1u;
@@ -192,8 +195,11 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     const float h_scale = exp2f(static_cast<float>(-p.h_exp));
     uint32_t item = 0;
     bool ok = true;
+    WorkItem w_next = {};
+    if (static_cast<int>(blockIdx.x) < n_work) w_next = p.work[blockIdx.x];
     for (int wi = blockIdx.x; ok && wi < n_work; wi += gridDim.x, ++item) {
-      const WorkItem w = p.work[wi];
+      const WorkItem w = w_next;
+      if (wi + static_cast<int>(gridDim.x) < n_work) w_next = p.work[wi + gridDim.x];  // in flight during the wait below
       const uint32_t d = item & 1u;
       if (!mbar_wait(dfull_bar(d), (item >> 1) & 1u, abort_flag, p.status, ST_WAIT_DFULL)) { ok = false; break; }
       tc_fence_after();

@@ -136,6 +136,109 @@ void free_layer(LayerWeights &w) {
 
 }  // namespace
 
+namespace moe {
+
+int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_bfloat16 *out_dev, unsigned flags,
+                 cudaStream_t s, const __nv_bfloat16 *t_local, int tp_rows_local) {
+  if (layer < 0 || layer >= c->L || !t || rows <= 0 || rows > c->max_rows)
+    return fail(c, MOE_ERR_INVALID, "moe_forward: layer %d rows %d (max %d)", layer, rows, c->max_rows);
+  if (!out_dev && !(flags & MOE_FWD_PARTIAL_F32)) return fail(c, MOE_ERR_INVALID, "moe_forward: null output");
+  LayerWeights &w = c->layers[layer];
+  if (!w.loaded) return fail(c, MOE_ERR_STATE, "layer %d has no weights", layer);
+  CU_TRY(c, cudaSetDevice(c->cfg.device));
+  const bool tpcall = tp_rows_local > 0;
+  const int tp = c->cfg.tp_size, rank = c->cfg.tp_rank;
+  const int T = rows, P = rows * c->K, E = c->E, H = c->H, K = c->K;
+  const int n_nt1 = (c->R1 + kTileN - 1) / kTileN, n_nt2 = (H + kTileN - 1) / kTileN;
+
+  CU_TRY(c, cudaMemsetAsync(c->counts, 0, sizeof(int) * E, s));
+  auto mark = [&]() {
+    if (!c->profiling) return;
+    cudaEvent_t ev;
+    if (!c->prof_pool.empty()) { ev = c->prof_pool.back(); c->prof_pool.pop_back(); }
+    else if (cudaEventCreate(&ev) != cudaSuccess) return;
+    cudaEventRecord(ev, s);
+    c->prof_events.push_back(ev);
+  };
+  mark();
+  if (!tpcall) {
+    const int splits = router_splits(T, H, c->sm_count);
+    launch_router_partials(t, w.router_w3, c->router_part, T, H, E, splits, s);
+    mark();
+    launch_topk_softmax(c->logits, c->router_part, splits, w.router_b, T, E, K, c->topk_idx, c->topk_w, c->counts, s);
+    mark();
+  } else {
+    // all-gather push of this rank's rows on the side stream, beside the routing of the same rows
+    ++c->tp_epoch;
+    CU_TRY(c, cudaEventRecord(c->ev_fork, s));
+    CU_TRY(c, cudaStreamWaitEvent(c->aux_stream, c->ev_fork, 0));
+    launch_tp_allgather_push(t_local, tp_rows_local, H, c->peers, tp, rank, c->sm_count, c->aux_stream);
+    CU_TRY(c, cudaEventRecord(c->ev_join, c->aux_stream));
+    const int splits = router_splits(tp_rows_local, H, c->sm_count);
+    launch_router_partials(t_local, w.router_w3, c->router_part, tp_rows_local, H, E, splits, s);
+    mark();
+    launch_topk_softmax(c->logits, c->router_part, splits, w.router_b, tp_rows_local, E, K, nullptr, nullptr, nullptr, s,
+                        tp, &c->peers, rank * tp_rows_local);
+    CU_TRY(c, cudaStreamWaitEvent(s, c->ev_join, 0));
+    launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, 0, c->tp_epoch, c->status, s);
+    launch_count_experts(c->topk_idx, T * K, E, c->counts, s);
+    mark();
+    c->launches += 3;
+  }
+  launch_build_index(c->topk_idx, c->counts, T, E, K, n_nt1, n_nt2, c->offsets, c->tile_base, c->pair_row,
+                     c->row_token, c->work1, c->work2, c->n_work, c->max_work1, c->max_work2, c->status, s);
+  mark();
+  if (flags & MOE_FWD_SIMT_GEMM) launch_gather_rows(t, c->row_token, c->offsets, E, c->xperm, H, P, s);
+  else launch_quantize_rows(t, c->row_token, c->offsets, c->tile_base, E, c->xq, c->sfa_x, H, P, s);
+  mark();
+  const int add_b2 = c->cfg.tp_rank == 0 ? 1 : 0;
+  if (flags & MOE_FWD_SIMT_GEMM) {
+    launch_simt_mlp1(w.w1_codes, c->pitch1, w.w1_scales_raw, w.b1, c->xperm, c->offsets, E, H, c->R1, c->hbuf,
+                     c->cfg.swiglu_limit, c->cfg.swiglu_alpha, P, s);
+    mark();
+    launch_simt_mlp2(w.w2_codes, c->pitch2, w.w2_scales_raw, w.b2, add_b2, c->hbuf, c->offsets, E, c->Dl, H,
+                     c->ybuf, P, s);
+  } else {
+    GemmArgs a{};
+    a.work = c->work1; a.n_work = c->n_work; a.K = H; a.R = c->R1;
+    a.n_kchunks = (H + kChunkK - 1) / kChunkK; a.n_ntiles = n_nt1;
+    a.sfb = w.w1_scales; a.sfa = c->sfa_x; a.sfa_tile_stride = kSfAtomBytes; a.bias = w.b1; a.add_bias = 1;
+    a.hq_out = c->hq; a.y_out = nullptr; a.ld_out = c->Dl; a.h_exp = c->h_exp;
+    a.limit = c->cfg.swiglu_limit; a.alpha = c->cfg.swiglu_alpha; a.status = c->status;
+    launch_expert_gemm_mlp1(w.tm_w1, c->tm_x1, a, c->sm_count, s);
+    mark();
+    GemmArgs b = a;
+    b.work = c->work2; b.n_work = c->n_work + 1; b.K = c->Dl; b.R = H;
+    b.n_kchunks = (c->Dl + kChunkK - 1) / kChunkK; b.n_ntiles = n_nt2;
+    b.sfb = w.w2_scales; b.sfa = c->sfa_h; b.sfa_tile_stride = 0; b.bias = w.b2; b.add_bias = add_b2;
+    b.hq_out = nullptr; b.y_out = c->ybuf; b.ld_out = H;
+    launch_expert_gemm_mlp2(w.tm_w2, c->tm_x2, b, c->sm_count, s);
+  }
+  mark();
+  if (!tpcall) {
+    const bool partial = (flags & MOE_FWD_PARTIAL_F32) != 0;
+    const bool keep_f32 = partial || (c->cfg.flags & MOE_CFG_KEEP_F32_OUT);
+    launch_combine(c->ybuf, c->topk_idx, c->topk_w, c->pair_row, T, H, K, partial ? nullptr : out_dev,
+                   keep_f32 ? c->out_f32 : nullptr, s);
+    mark();
+  } else {
+    // send half of the reduce-scatter inside the combine; then wait for every peer's rows and add the slots
+    launch_combine(c->ybuf, c->topk_idx, c->topk_w, c->pair_row, T, H, K, c->tp_partial,
+                   (c->cfg.flags & MOE_CFG_KEEP_F32_OUT) ? c->out_f32 : nullptr, s, tp, &c->peers, tp_rows_local, rank);
+    ++c->tp_epoch_rs;
+    launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, 1, c->tp_epoch_rs, c->status, s);
+    launch_tp_sum_slots(c->tp_partial, tp, tp_rows_local, H, out_dev, c->sm_count, s);
+    mark();
+    c->launches += 2;
+  }
+  c->launches += 7;
+  c->last_rows = rows;
+  CU_TRY(c, cudaGetLastError());
+  return MOE_OK;
+}
+
+}  // namespace moe
+
 extern "C" {
 
 const char *moe_strerror(int code) {
@@ -219,7 +322,12 @@ int moe_create(const moe_config *cfg, moe_handle *out) {
   c->peers.gather[cfg->tp_rank] = c->t_in;
   c->peers.partial[cfg->tp_rank] = c->tp_partial;
   c->peers.flags[cfg->tp_rank] = c->tp_flags;
-  c->tp_attached |= 7u << (3 * cfg->tp_rank);
+  c->peers.topk_idx[cfg->tp_rank] = c->topk_idx;
+  c->peers.topk_w[cfg->tp_rank] = c->topk_w;
+  c->tp_attached |= ((1ull << kTpBufs) - 1) << (kTpBufs * cfg->tp_rank);
+  CU_TRY(c, cudaStreamCreateWithFlags(&c->aux_stream, cudaStreamNonBlocking));
+  CU_TRY(c, cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming));
+  CU_TRY(c, cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming));
   const int n_nt1 = (c->R1 + kTileN - 1) / kTileN, n_nt2 = (c->H + kTileN - 1) / kTileN;
   c->max_tiles = c->max_pairs / kTokTile + c->E + 1;
   c->max_work1 = c->max_tiles * n_nt1;
@@ -265,6 +373,9 @@ int moe_destroy(moe_handle c) {
   cudaSetDevice(c->cfg.device);
   if (c->stream) { cudaStreamSynchronize(c->stream); cudaStreamDestroy(c->stream); }
   for (void *p : c->ipc_opened) cudaIpcCloseMemHandle(p);
+  if (c->aux_stream) { cudaStreamSynchronize(c->aux_stream); cudaStreamDestroy(c->aux_stream); }
+  if (c->ev_fork) cudaEventDestroy(c->ev_fork);
+  if (c->ev_join) cudaEventDestroy(c->ev_join);
   cudaFree(c->tp_partial); cudaFree(c->tp_flags);
   for (auto &w : c->layers) free_layer(w);
   for (cudaEvent_t e : c->prof_events) cudaEventDestroy(e);
@@ -376,71 +487,8 @@ int moe_route_topk(moe_handle c, const float *logits_dev, int rows, int *idx_dev
 
 int moe_forward(moe_handle c, int layer, const void *t_dev, int rows, void *out_dev, unsigned flags, void *stream) {
   if (!c) return MOE_ERR_INVALID;
-  if (layer < 0 || layer >= c->L || !t_dev || rows <= 0 || rows > c->max_rows)
-    return fail(c, MOE_ERR_INVALID, "moe_forward: layer %d rows %d (max %d)", layer, rows, c->max_rows);
-  if (!out_dev && !(flags & MOE_FWD_PARTIAL_F32)) return fail(c, MOE_ERR_INVALID, "moe_forward: null output");
-  LayerWeights &w = c->layers[layer];
-  if (!w.loaded) return fail(c, MOE_ERR_STATE, "layer %d has no weights", layer);
-  CU_TRY(c, cudaSetDevice(c->cfg.device));
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int T = rows, P = rows * c->K, E = c->E, H = c->H, K = c->K;
-  const __nv_bfloat16 *t = static_cast<const __nv_bfloat16 *>(t_dev);
-  const int n_nt1 = (c->R1 + kTileN - 1) / kTileN, n_nt2 = (H + kTileN - 1) / kTileN;
-
-  CU_TRY(c, cudaMemsetAsync(c->counts, 0, sizeof(int) * E, s));
-  auto mark = [&]() {
-    if (!c->profiling) return;
-    cudaEvent_t ev;
-    if (!c->prof_pool.empty()) { ev = c->prof_pool.back(); c->prof_pool.pop_back(); }
-    else if (cudaEventCreate(&ev) != cudaSuccess) return;
-    cudaEventRecord(ev, s);
-    c->prof_events.push_back(ev);
-  };
-  mark();
-  const int splits = router_splits(T, H, c->sm_count);
-  launch_router_partials(t, w.router_w3, c->router_part, T, H, E, splits, s);
-  mark();
-  launch_topk_softmax(c->logits, c->router_part, splits, w.router_b, T, E, K, c->topk_idx, c->topk_w, c->counts, s);
-  mark();
-  launch_build_index(c->topk_idx, c->counts, T, E, K, n_nt1, n_nt2, c->offsets, c->tile_base, c->pair_row,
-                     c->row_token, c->work1, c->work2, c->n_work, c->max_work1, c->max_work2, c->status, s);
-  mark();
-  if (flags & MOE_FWD_SIMT_GEMM) launch_gather_rows(t, c->row_token, c->offsets, E, c->xperm, H, P, s);
-  else launch_quantize_rows(t, c->row_token, c->offsets, c->tile_base, E, c->xq, c->sfa_x, H, P, s);
-  mark();
-  const int add_b2 = c->cfg.tp_rank == 0 ? 1 : 0;
-  if (flags & MOE_FWD_SIMT_GEMM) {
-    launch_simt_mlp1(w.w1_codes, c->pitch1, w.w1_scales_raw, w.b1, c->xperm, c->offsets, E, H, c->R1, c->hbuf,
-                     c->cfg.swiglu_limit, c->cfg.swiglu_alpha, P, s);
-    mark();
-    launch_simt_mlp2(w.w2_codes, c->pitch2, w.w2_scales_raw, w.b2, add_b2, c->hbuf, c->offsets, E, c->Dl, H,
-                     c->ybuf, P, s);
-  } else {
-    GemmArgs a{};
-    a.work = c->work1; a.n_work = c->n_work; a.K = H; a.R = c->R1;
-    a.n_kchunks = (H + kChunkK - 1) / kChunkK; a.n_ntiles = n_nt1;
-    a.sfb = w.w1_scales; a.sfa = c->sfa_x; a.sfa_tile_stride = kSfAtomBytes; a.bias = w.b1; a.add_bias = 1;
-    a.hq_out = c->hq; a.y_out = nullptr; a.ld_out = c->Dl; a.h_exp = c->h_exp;
-    a.limit = c->cfg.swiglu_limit; a.alpha = c->cfg.swiglu_alpha; a.status = c->status;
-    launch_expert_gemm_mlp1(w.tm_w1, c->tm_x1, a, c->sm_count, s);
-    mark();
-    GemmArgs b = a;
-    b.work = c->work2; b.n_work = c->n_work + 1; b.K = c->Dl; b.R = H;
-    b.n_kchunks = (c->Dl + kChunkK - 1) / kChunkK; b.n_ntiles = n_nt2;
-    b.sfb = w.w2_scales; b.sfa = c->sfa_h; b.sfa_tile_stride = 0; b.bias = w.b2; b.add_bias = add_b2;
-    b.hq_out = nullptr; b.y_out = c->ybuf; b.ld_out = H;
-    launch_expert_gemm_mlp2(w.tm_w2, c->tm_x2, b, c->sm_count, s);
-  }
-  mark();
-  const bool partial = (flags & MOE_FWD_PARTIAL_F32) != 0;
-  const bool keep_f32 = partial || (c->cfg.flags & MOE_CFG_KEEP_F32_OUT);
-  launch_combine(c->ybuf, c->topk_idx, c->topk_w, c->pair_row, T, H, K,
-                 partial ? nullptr : static_cast<__nv_bfloat16 *>(out_dev), keep_f32 ? c->out_f32 : nullptr, s);
-  mark();
-  c->launches += 7;
-  c->last_rows = rows;
-  CU_TRY(c, cudaGetLastError());
-  return MOE_OK;
+  return forward_impl(c, layer, static_cast<const __nv_bfloat16 *>(t_dev), rows, static_cast<__nv_bfloat16 *>(out_dev),
+                      flags, static_cast<cudaStream_t>(stream), nullptr, 0);
 }
 
 int moe_synchronize(moe_handle c) {

@@ -42,7 +42,10 @@ struct TpPeers {
   void *gather[kMaxTp];       // bf16 [max_rows, H]: all-gather destination (gather_x_g)
   void *partial[kMaxTp];      // bf16 [max_rows, H]: this rank's partial block output (e_agg_g)
   uint32_t *flags[kMaxTp];    // [2 phases][kMaxTp] epoch words
+  void *topk_idx[kMaxTp];     // i32 [max_rows, K]: every rank routes its own rows and writes them to all (topk_i_g)
+  void *topk_w[kMaxTp];       // f32 [max_rows, K]                                                  (topk_v_g)
 };
+constexpr int kTpBufs = 5;
 
 // One work item of the grouped GEMM.
 struct __align__(16) WorkItem {
@@ -135,7 +138,9 @@ struct moe_ctx {
   moe::TpPeers peers = {};          // TP group view; own entries are set at creation
   __nv_bfloat16 *tp_partial = nullptr;  // this rank's bf16 partial output [max_rows, H]
   uint32_t *tp_flags = nullptr;     // [2][kMaxTp], written by the peers
-  unsigned tp_attached = 0;         // bit (3*r + which) set once rank r's buffer `which` is known
+  uint64_t tp_attached = 0;         // bit (kTpBufs*r + which) set once rank r's buffer `which` is known
+  cudaStream_t aux_stream = nullptr;  // the all-gather push runs beside the router
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
   uint32_t tp_epoch = 0, tp_epoch_rs = 0;  // all-gather / reduce-scatter call counters
   std::vector<void *> ipc_opened;   // mappings to close at destroy
   bool profiling = false;
@@ -151,7 +156,9 @@ int router_splits(int T, int H, int sm_count);
 void launch_router_partials(const __nv_bfloat16 *t, const __nv_bfloat16 *w3, float *partial, int T, int H, int E,
                             int splits, cudaStream_t s);
 void launch_topk_softmax(float *logits, const float *partial, int splits, const float *bias, int T, int E, int K,
-                         int *idx, float *w, int *counts, cudaStream_t s);
+                         int *idx, float *w, int *counts, cudaStream_t s, int tp = 0, const TpPeers *peers = nullptr,
+                         int row_offset = 0);
+void launch_count_experts(const int *idx, int n, int E, int *counts, cudaStream_t s);
 void launch_build_index(const int *topk_idx, const int *counts, int T, int E, int K, int n_ntiles1, int n_ntiles2,
                         int *offsets, int *tile_base, int *pair_row, int *row_token, WorkItem *work1,
                         WorkItem *work2, int *n_work, int max_work1, int max_work2, unsigned int *status,
@@ -161,7 +168,8 @@ void launch_quantize_rows(const __nv_bfloat16 *t, const int *row_token, const in
 void launch_gather_rows(const __nv_bfloat16 *t, const int *row_token, const int *offsets, int E, __half *xperm,
                         int H, int max_pairs, cudaStream_t s);
 void launch_combine(const float *y, const int *topk_idx, const float *topk_w, const int *pair_row, int T, int H,
-                    int K, __nv_bfloat16 *out_bf16, float *out_f32, cudaStream_t s);
+                    int K, __nv_bfloat16 *out_bf16, float *out_f32, cudaStream_t s, int tp = 0,
+                    const TpPeers *peers = nullptr, int rows_local = 0, int rank = 0);
 
 // expert_gemm_sm100.cu
 cudaError_t expert_gemm_init();
@@ -175,6 +183,8 @@ void launch_tp_allgather_push(const __nv_bfloat16 *src, int rows_local, int H, c
                               int sm_count, cudaStream_t s);
 void launch_tp_signal_wait(const TpPeers &peers, uint32_t *my_flags, int tp, int rank, int phase, uint32_t epoch,
                            unsigned int *status, cudaStream_t s);
+void launch_tp_sum_slots(const __nv_bfloat16 *landing, int tp, int rows_local, int H, __nv_bfloat16 *out, int sm_count,
+                         cudaStream_t s);
 void launch_tp_reduce_scatter_pull(const TpPeers &peers, int tp, int rank, int rows_local, int H, __nv_bfloat16 *out,
                                    int sm_count, cudaStream_t s);
 
@@ -185,5 +195,11 @@ void launch_simt_mlp1(const uint8_t *codes, int pitch, const uint8_t *scales_raw
 void launch_simt_mlp2(const uint8_t *codes, int pitch, const uint8_t *scales_raw, const __nv_bfloat16 *bias,
                       int add_bias, const __half *h, const int *offsets, int E, int Dl, int H, float *y_out,
                       int n_rows, cudaStream_t s);
+
+// moe_api.cu: the block itself.  With tp_rows_local > 0 this is a call of a tensor-parallel group: t is the
+// gather buffer, t_local this rank's rows; routing is computed for the local rows only and exchanged, the
+// combine pushes each row's partial to the rank that owns it, and out_dev receives this rank's summed rows.
+int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int T, __nv_bfloat16 *out_dev, unsigned flags,
+                 cudaStream_t s, const __nv_bfloat16 *t_local, int tp_rows_local);
 
 }  // namespace moe

@@ -26,14 +26,16 @@ void **slot(moe_ctx *c, int which, int rank) {
     case MOE_TP_BUF_GATHER: return &c->peers.gather[rank];
     case MOE_TP_BUF_PARTIAL: return &c->peers.partial[rank];
     case MOE_TP_BUF_FLAGS: return reinterpret_cast<void **>(&c->peers.flags[rank]);
+    case MOE_TP_BUF_TOPK_IDX: return &c->peers.topk_idx[rank];
+    case MOE_TP_BUF_TOPK_W: return &c->peers.topk_w[rank];
     default: return nullptr;
   }
 }
 
 bool group_complete(const moe_ctx *c) {
   for (int r = 0; r < c->cfg.tp_size; ++r)
-    for (int w = 0; w < 3; ++w)
-      if (!(c->tp_attached & (1u << (3 * r + w)))) return false;
+    for (int w = 0; w < kTpBufs; ++w)
+      if (!(c->tp_attached & (1ull << (kTpBufs * r + w)))) return false;
   return true;
 }
 
@@ -83,7 +85,7 @@ int moe_tp_attach_ipc(moe_handle c, int which, int rank, const void *handle_in) 
   if (e != cudaSuccess) return tp_fail(c, MOE_ERR_CUDA, "cudaIpcOpenMemHandle(rank %d): %s", rank, cudaGetErrorString(e));
   c->ipc_opened.push_back(p);
   *slot(c, which, rank) = p;
-  c->tp_attached |= 1u << (3 * rank + which);
+  c->tp_attached |= 1ull << (kTpBufs * rank + which);
   return MOE_OK;
 }
 
@@ -103,7 +105,7 @@ int moe_tp_attach_ptr(moe_handle c, int which, int rank, void *dev_ptr, int peer
     cudaGetLastError();
   }
   *slot(c, which, rank) = dev_ptr;
-  c->tp_attached |= 1u << (3 * rank + which);
+  c->tp_attached |= 1ull << (kTpBufs * rank + which);
   return MOE_OK;
 }
 
@@ -139,12 +141,12 @@ int moe_tp_reduce_scatter(moe_handle c, int rows_local, void *out_local, void *s
 int moe_tp_forward(moe_handle c, int layer, const void *t_local, int rows_local, void *out_local, unsigned flags,
                    void *stream) {
   if (!c || !t_local || !out_local) return MOE_ERR_INVALID;
-  int rc = moe_tp_allgather(c, t_local, rows_local, stream);
+  int rc = check_tp_call(c, rows_local, "moe_tp_forward");
   if (rc != MOE_OK) return rc;
-  const int T = rows_local * c->cfg.tp_size;
-  rc = moe_forward(c, layer, c->peers.gather[c->cfg.tp_rank], T, c->tp_partial, flags & ~MOE_FWD_PARTIAL_F32, stream);
-  if (rc != MOE_OK) return rc;
-  return moe_tp_reduce_scatter(c, rows_local, out_local, stream);
+  return forward_impl(c, layer, static_cast<const __nv_bfloat16 *>(c->peers.gather[c->cfg.tp_rank]),
+                      rows_local * c->cfg.tp_size, static_cast<__nv_bfloat16 *>(out_local),
+                      flags & ~MOE_FWD_PARTIAL_F32, static_cast<cudaStream_t>(stream),
+                      static_cast<const __nv_bfloat16 *>(t_local), rows_local);
 }
 
 int moe_tp_forward_host(moe_handle c, int layer, const void *t_local_host, int rows_local, void *out_local_host,

@@ -6,6 +6,7 @@
 // by build_index_kernel.
 #include <cuda_fp8.h>
 
+#include <algorithm>
 #include <cstdio>
 #include <mutex>
 
@@ -161,12 +162,16 @@ constexpr int kMaxTopK = 8;
 // With `partial` set, the logits are first formed from the router's split-k partial sums: slices added
 // in ascending order in double precision, rounded to float, then the bias added in float
 // (run.cpp:662-669), and written to `logits`.  Otherwise `logits` is the input.
+// With tp > 0 the call routes rows [row_offset, row_offset + T) of a tensor-parallel group's union batch:
+// logits go to those rows of `logits`, and the selection is written into the top-k buffers of every rank
+// of the group (peer stores), so that no rank repeats another rank's routing.
 __global__ void topk_softmax_kernel(float *__restrict__ logits, const float *__restrict__ partial, int splits,
                                     const float *__restrict__ bias, int T, int E, int K, int *__restrict__ idx,
-                                    float *__restrict__ w, int *__restrict__ counts) {
+                                    float *__restrict__ w, int *__restrict__ counts, int tp, TpPeers peers,
+                                    int row_offset) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= T) return;
-  float *row = logits + static_cast<size_t>(warp) * E;
+  float *row = logits + static_cast<size_t>(row_offset + warp) * E;
   float v[kMaxExpPerLane];
   unsigned taken = 0;
 #pragma unroll
@@ -217,17 +222,50 @@ __global__ void topk_softmax_kernel(float *__restrict__ logits, const float *__r
   double sum = 0.0;
   for (int k = 0; k < K; ++k) sum += static_cast<double>(__shfl_sync(0xffffffffu, ex, k));
   if (lane < K) {
-    idx[static_cast<size_t>(warp) * K + lane] = sel_i;
-    w[static_cast<size_t>(warp) * K + lane] = static_cast<float>(static_cast<double>(ex) / sum);
+    const float wt = static_cast<float>(static_cast<double>(ex) / sum);
+    const size_t o = static_cast<size_t>(row_offset + warp) * K + lane;
+    if (tp > 0) {
+      for (int r = 0; r < tp; ++r) {
+        static_cast<int *>(peers.topk_idx[r])[o] = sel_i;
+        static_cast<float *>(peers.topk_w[r])[o] = wt;
+      }
+    } else {
+      idx[o] = sel_i;
+      w[o] = wt;
+    }
     if (counts != nullptr && sel_i >= 0) atomicAdd(&counts[sel_i], 1);
   }
 }
 
+// Expert histogram over an already exchanged selection (count_tokens_per_expert_kernel,
+// kernels/moe.hpp:744); block-local bins first, so global atomics are E per block.
+__global__ void __launch_bounds__(256) count_experts_kernel(const int *__restrict__ idx, int n, int E,
+                                                            int *__restrict__ counts) {
+  __shared__ int bins[256];
+  for (int i = threadIdx.x; i < E; i += blockDim.x) bins[i] = 0;
+  __syncthreads();
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const int e = idx[i];
+    if (e >= 0 && e < E) atomicAdd(&bins[e], 1);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < E; i += blockDim.x)
+    if (bins[i]) atomicAdd(&counts[i], bins[i]);
+}
+
+void launch_count_experts(const int *idx, int n, int E, int *counts, cudaStream_t s) {
+  const int blocks = std::max(1, std::min(64, (n + 1023) / 1024));
+  count_experts_kernel<<<blocks, 256, 0, s>>>(idx, n, E, counts);
+}
+
 void launch_topk_softmax(float *logits, const float *partial, int splits, const float *bias, int T, int E, int K,
-                         int *idx, float *w, int *counts, cudaStream_t s) {
+                         int *idx, float *w, int *counts, cudaStream_t s, int tp, const TpPeers *peers, int row_offset) {
   const int threads = 128;
   const int blocks = (T * 32 + threads - 1) / threads;
-  topk_softmax_kernel<<<blocks, threads, 0, s>>>(logits, partial, splits, bias, T, E, K, idx, w, counts);
+  TpPeers pv = {};
+  if (tp > 0 && peers != nullptr) pv = *peers;
+  topk_softmax_kernel<<<blocks, threads, 0, s>>>(logits, partial, splits, bias, T, E, K, idx, w, counts, tp, pv,
+                                                 row_offset);
 }
 
 // ---------------------------------------------------------------------------
@@ -468,8 +506,13 @@ void launch_gather_rows(const __nv_bfloat16 *t, const int *row_token, const int 
 __global__ void __launch_bounds__(256)
 combine_kernel(const float *__restrict__ y, const int *__restrict__ topk_idx, const float *__restrict__ topk_w,
                const int *__restrict__ pair_row, int T, int H, int K, __nv_bfloat16 *__restrict__ out_bf16,
-               float *__restrict__ out_f32) {
+               float *__restrict__ out_f32, int tp, TpPeers peers, int rows_local, int rank) {
   const int t = blockIdx.x;
+  // tensor-parallel call: the row's bf16 partial goes straight into slot `rank` of the landing buffer of the
+  // rank that owns row t (a peer store over NVLink), which is the send half of the reduce-scatter
+  if (tp > 0)
+    out_bf16 = static_cast<__nv_bfloat16 *>(peers.partial[t / rows_local]) +
+               (static_cast<ptrdiff_t>(rank) * rows_local + (t % rows_local) - t) * static_cast<ptrdiff_t>(H);
   int ex[kMaxTopK], row[kMaxTopK];
   float wt[kMaxTopK];
   for (int k = 0; k < K; ++k) {
@@ -504,8 +547,11 @@ combine_kernel(const float *__restrict__ y, const int *__restrict__ topk_idx, co
 }
 
 void launch_combine(const float *y, const int *topk_idx, const float *topk_w, const int *pair_row, int T, int H,
-                    int K, __nv_bfloat16 *out_bf16, float *out_f32, cudaStream_t s) {
-  combine_kernel<<<T, 256, 0, s>>>(y, topk_idx, topk_w, pair_row, T, H, K, out_bf16, out_f32);
+                    int K, __nv_bfloat16 *out_bf16, float *out_f32, cudaStream_t s, int tp, const TpPeers *peers,
+                    int rows_local, int rank) {
+  TpPeers pv = {};
+  if (tp > 0 && peers != nullptr) pv = *peers;
+  combine_kernel<<<T, 256, 0, s>>>(y, topk_idx, topk_w, pair_row, T, H, K, out_bf16, out_f32, tp, pv, rows_local, rank);
 }
 
 // ---------------------------------------------------------------------------

@@ -88,6 +88,42 @@ tp_reduce_scatter_pull_kernel(TpPeers peers, int tp, size_t slot_vec, size_t n_v
   }
 }
 
+// out[i] = bf16( sum over slots s = 0..tp-1 of landing[s][i] ): the receive half of the reduce-scatter when
+// every rank has pushed its partial rows into this rank's landing buffer (fp32 adds in rank order).
+__global__ void __launch_bounds__(256)
+tp_sum_slots_kernel(const uint4 *__restrict__ landing, int tp, size_t n_vec, uint4 *__restrict__ out) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int r = 0; r < tp; ++r) {
+      const uint4 v = landing[static_cast<size_t>(r) * n_vec + i];
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[2 * j] += __uint_as_float(w[j] << 16);
+        acc[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u);
+      }
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __nv_bfloat162 b = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+      o[j] = *reinterpret_cast<const uint32_t *>(&b);
+    }
+    out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+void launch_tp_sum_slots(const __nv_bfloat16 *landing, int tp, int rows_local, int H, __nv_bfloat16 *out, int sm_count,
+                         cudaStream_t s) {
+  const size_t n_vec = static_cast<size_t>(rows_local) * H / 8;
+  const int blocks = static_cast<int>(std::min<size_t>((n_vec + 255) / 256, static_cast<size_t>(sm_count) * 4));
+  tp_sum_slots_kernel<<<std::max(blocks, 1), 256, 0, s>>>(reinterpret_cast<const uint4 *>(landing), tp, n_vec,
+                                                          reinterpret_cast<uint4 *>(out));
+}
+
 void launch_tp_allgather_push(const __nv_bfloat16 *src, int rows_local, int H, const TpPeers &peers, int tp, int rank,
                               int sm_count, cudaStream_t s) {
   const size_t n_vec = static_cast<size_t>(rows_local) * H / 8;

@@ -108,11 +108,14 @@ int moe_route_topk(moe_handle h, const float *logits_dev, int rows, int *idx_dev
 
 /* ---- tensor-parallel group (replaces TPGroup / tp_init / tp_enable_p2p, getp-csrc/nccl.hpp:25-98, and
  * the raw peer pointers the reference reads through gpu_transformers[], getp_run.cpp:2594,:2965,:3221).
- * A handle created with tp_size > 1 owns three symmetric buffers; every rank must learn every peer's. */
+ * A handle created with tp_size > 1 owns MOE_TP_N_BUFS symmetric buffers; every rank must learn every peer's. */
 enum {
   MOE_TP_BUF_GATHER = 0,  /* bf16 [max_rows, H]  all-gather destination        (gather_x_g) */
   MOE_TP_BUF_PARTIAL = 1, /* bf16 [max_rows, H]  this rank's partial output    (e_agg_g)    */
-  MOE_TP_BUF_FLAGS = 2    /* u32  [2][8]         arrival epochs written by the peers        */
+  MOE_TP_BUF_FLAGS = 2,   /* u32  [2][8]         arrival epochs written by the peers        */
+  MOE_TP_BUF_TOPK_IDX = 3,/* i32  [max_rows, K]  expert choice of every row of the union    (topk_i_g)  */
+  MOE_TP_BUF_TOPK_W = 4,  /* f32  [max_rows, K]  routing weights of every row of the union  (topk_v_g)  */
+  MOE_TP_N_BUFS = 5
 };
 #define MOE_TP_HANDLE_BYTES 64 /* sizeof(cudaIpcMemHandle_t) */
 /* Ranks in different processes: export, exchange the 64 bytes by any channel, attach. */

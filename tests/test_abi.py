@@ -72,3 +72,24 @@ def test_algorithmic_work_matches_published_formula(synth):
     assert flops == 1856 * (199065600 + 2 * 2880 * 128)
     assert synth.weight_bytes_per_expert(2880, 2880) == 13236480
     assert nbytes == 128 * 13236480 + 1856 * 2880 * 4 + 128 * 2880 * 4
+
+
+def test_cpp_shim_compiles_and_links(tmp_path):
+    """include/moe_b200_shim.hpp (the reference's entry-point names on top of the C ABI) builds
+    with the host compiler and its host-only helpers agree with the library."""
+    import shutil
+    import subprocess
+    src = tmp_path / "shim.cpp"
+    src.write_text('#include "moe_b200_shim.hpp"\n'
+                   'int main() { TPGroup tp; tp_init(tp, 8, 5, 4); int s, n; mlp1_shard(5760, 4, 1, s, n);\n'
+                   '  int a, b; mlp2_shard_input(2880, 4, 3, a, b);\n'
+                   '  return (tp.group_id == 1 && tp.rank_in_group == 1 && tp.group_devs[3] == 7 && s == 1472 && n == 1472\n'
+                   '          && a == 2176 && b == 704) ? 0 : 1; }\n')
+    gxx = shutil.which("g++")
+    if gxx is None or not os.path.exists("/usr/local/cuda/include/cuda_runtime.h"):
+        pytest.skip("no host compiler or CUDA headers")
+    exe = tmp_path / "shim"
+    libdir = os.path.join(ROOT, "gpt-oss_b200")
+    subprocess.run([gxx, "-std=c++17", "-I" + os.path.join(ROOT, "include"), "-I/usr/local/cuda/include", str(src),
+                    "-L" + libdir, "-lmoe_b200", "-Wl,-rpath," + libdir, "-o", str(exe)], check=True)
+    assert subprocess.run([str(exe)]).returncode == 0
