@@ -25,7 +25,7 @@
 // expanded to the 8-bit containers the MMA reads, 128-byte swizzle), weight
 // scales (two 512-byte atoms, pre-tiled at load time), activations [128 rows x
 // 128] e4m3 (TMA, 128-byte swizzle).  The MMA thread copies the scale atoms to
-// tensor memory (tcgen05.cp) and issues four K = 32 instructions.  Eight
+// tensor memory (tcgen05.cp) and issues four K = 32 instructions.  Sixteen
 // epilogue warps drain the fp32 accumulator (double buffered: 2 x 240 columns).
 // No cluster launch, no multicast: every CTA fetches its own tiles.
 #include <cuda_fp8.h>
@@ -44,14 +44,16 @@ constexpr int kWBytes = kTileNPad * kChunkK;      // 32768: 256 rows x 128 conta
 // the transaction count of a 16U4_ALIGN16B copy is the PACKED size: 240 rows x 64 bytes
 constexpr int kWLoadBytes = kTileN * kChunkK / 2; // 15360
 constexpr int kStageBytes = kABytes + kWBytes + kSfbChunkBytes;  // 50176
-constexpr int kSfaOff = kStages * kStageBytes;    // two per-item activation scale atoms
-constexpr int kBarOff = kSfaOff + 2 * kSfAtomBytes;
-constexpr int kNumBars = 2 * kStages + 6;         // full, empty, d_full[2], d_empty[2], sfa_full[2]
+constexpr int kSfaSlots = 4;                      // per-item activation scale atoms, a ring of their own
+constexpr int kSfaOff = kStages * kStageBytes;
+constexpr int kBarOff = kSfaOff + kSfaSlots * kSfAtomBytes;
+constexpr int kNumBars = 2 * kStages + 4 + 2 * kSfaSlots;  // full, empty, d_full[2], d_empty[2], sfa_full, sfa_empty
 constexpr int kSmemBytes = kBarOff + 8 * kNumBars + 16 + 1024 /*alignment slack*/;
 
-constexpr int kEpiWarps = 8;
-constexpr int kProducerWarp = 8, kMmaWarp = 9;
-constexpr int kThreads = 10 * 32;
+constexpr int kEpiWarps = 16;             // four per tensor-memory lane quadrant
+constexpr int kEpiChunks = 4;             // 16-column chunks per epilogue warp (15 in all)
+constexpr int kProducerWarp = 16, kMmaWarp = 17;
+constexpr int kThreads = 18 * 32;
 
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kAccBufCols = kTileN;          // accumulator buffer d at columns d*240
@@ -86,7 +88,8 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
   auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
   auto dfull_bar = [&](int d) { return bar_base + 8u * (2 * kStages + d); };
   auto dempty_bar = [&](int d) { return bar_base + 8u * (2 * kStages + 2 + d); };
-  auto sfa_bar = [&](int d) { return bar_base + 8u * (2 * kStages + 4 + d); };
+  auto sfa_full_bar = [&](int q) { return bar_base + 8u * (2 * kStages + 4 + q); };
+  auto sfa_empty_bar = [&](int q) { return bar_base + 8u * (2 * kStages + 4 + kSfaSlots + q); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -95,8 +98,8 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     for (int d = 0; d < 2; ++d) {
       mbar_init(dfull_bar(d), 1);
       mbar_init(dempty_bar(d), kEpiWarps);
-      mbar_init(sfa_bar(d), 1);
     }
+    for (int q = 0; q < kSfaSlots; ++q) { mbar_init(sfa_full_bar(q), 1); mbar_init(sfa_empty_bar(q), 1); }
     *abort_flag = 0u;
     fence_mbar_init();
     fence_proxy_async_smem();
@@ -128,13 +131,13 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       for (int wi = blockIdx.x; ok && wi < n_work; wi += gridDim.x, ++item) {
         const WorkItem w = w_next;
         if (wi + static_cast<int>(gridDim.x) < n_work) w_next = p.work[wi + gridDim.x];
-        // activation scale atom of this token tile; its slot is free once the MMAs of item-2 are done,
-        // which the accumulator hand-over of that item (d_empty) has already implied
-        const uint32_t d = item & 1u;
-        if (!mbar_wait(dempty_bar(d), ((item >> 1) & 1u) ^ 1u, abort_flag, p.status, ST_WAIT_DEMPTY)) { ok = false; break; }
-        mbar_arrive_expect_tx(sfa_bar(d), kSfAtomBytes);
-        bulk_load(smem_base + kSfaOff + d * kSfAtomBytes, p.sfa + static_cast<size_t>(w.tile) * p.sfa_tile_stride,
-                  kSfAtomBytes, sfa_bar(d));
+        // activation scale atom of this token tile, through its own ring so that the producer never waits
+        // for an epilogue; a slot is free once the MMAs of the item that used it are done
+        const uint32_t q = item % kSfaSlots;
+        if (!mbar_wait(sfa_empty_bar(q), ((item / kSfaSlots) & 1u) ^ 1u, abort_flag, p.status, ST_WAIT_EMPTY)) { ok = false; break; }
+        mbar_arrive_expect_tx(sfa_full_bar(q), kSfAtomBytes);
+        bulk_load(smem_base + kSfaOff + q * kSfAtomBytes, p.sfa + static_cast<size_t>(w.tile) * p.sfa_tile_stride,
+                  kSfAtomBytes, sfa_full_bar(q));
         const uint8_t *sfb_src = p.sfb + (static_cast<size_t>(w.expert) * p.n_ntiles + w.ntile) * nkc * kSfbChunkBytes;
         for (int kc = 0; kc < nkc; ++kc, ++it) {
           const int s = it % kStages;
@@ -159,10 +162,11 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       for (int wi = blockIdx.x; ok && wi < n_work; wi += gridDim.x, ++item) {
         const uint32_t d = item & 1u;
         if (!mbar_wait(dempty_bar(d), ((item >> 1) & 1u) ^ 1u, abort_flag, p.status, ST_WAIT_DEMPTY)) { ok = false; break; }
-        if (!mbar_wait(sfa_bar(d), (item >> 1) & 1u, abort_flag, p.status, ST_WAIT_AREADY)) { ok = false; break; }
+        const uint32_t q = item % kSfaSlots;
+        if (!mbar_wait(sfa_full_bar(q), (item / kSfaSlots) & 1u, abort_flag, p.status, ST_WAIT_AREADY)) { ok = false; break; }
         tc_fence_after();
         const uint32_t sfa_t = tmem_base + kSfaCol0 + 4 * d;
-        tmem_cp_sf_atom(sfa_t, smem_base + kSfaOff + d * kSfAtomBytes);
+        tmem_cp_sf_atom(sfa_t, smem_base + kSfaOff + q * kSfAtomBytes);
         const uint32_t d_addr = tmem_base + d * kAccBufCols;
         for (int kc = 0; ok && kc < nkc; ++kc, ++it) {
           const int s = it % kStages;
@@ -180,13 +184,16 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
           }
           mma_commit(empty_bar(s));
         }
-        if (ok) mma_commit(dfull_bar(d));
+        if (ok) {
+          mma_commit(dfull_bar(d));
+          mma_commit(sfa_empty_bar(q));
+        }
       }
     }
   } else {
     // ------------------------------------------------------------- epilogue warps
     // Warp w reads tensor-memory lanes 32*(w%4).., i.e. accumulator rows 32q + l: token 16q + l/2, high
-    // (even l) or low (odd l) term.  Warps 0-3 take the 16-column chunks 0..7, warps 4-7 chunks 8..14.
+    // (even l) or low (odd l) term.  Warps 4g..4g+3 take the 16-column chunks 4g..4g+3 (15 chunks in all).
     // Loads are software pipelined: chunk c+1 is in flight while chunk c is processed.
     const int quad = warp & 3, half = warp >> 2;
     const uint32_t lane_field = static_cast<uint32_t>(quad * 32) << 16;
@@ -208,34 +215,39 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       const __nv_bfloat16 *bias_row = p.bias + static_cast<size_t>(w.expert) * p.R;
       const uint32_t acc = tmem_base + lane_field + d * kAccBufCols;
       // chunks of this warp that hold rows of the matrix (rows past it are zero-filled and produce nothing)
-      const int c_beg = half * 8;
-      const int c_end = min(half ? kTileN / 16 : 8, (p.R - n0 + 15) / 16);
+      const int c_beg = half * kEpiChunks;
+      const int c_end = min(min(c_beg + kEpiChunks, kTileN / 16), (p.R - n0 + 15) / 16);
 
       auto process = [&](const uint32_t (&v)[16], int c0) {
-        // sum of the high and low partial products; afterwards even lanes own columns 0-7, odd lanes 8-15
+        // Sum of the high and low partial products of a token (adjacent lanes).  Each lane of the pair keeps 8
+        // of the 16 columns.  MLP1: even lane columns 0-7, odd lane 8-15 (whole gate/up pairs, 4 outputs each).
+        // MLP2: even lane columns 0-3 and 8-11, odd lane 4-7 and 12-15, so that the pair's two 16-byte stores
+        // of one instruction fill one 32-byte sector.
         float tot[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          const float first = __uint_as_float(v[i]), second = __uint_as_float(v[8 + i]);
-          const float mine = odd ? second : first;
-          const float give = odd ? first : second;
+          const int ce = (MODE == 1) ? i : (i < 4 ? i : i + 4);   // column the even lane keeps
+          const int co = (MODE == 1) ? i + 8 : ce + 4;            // column the odd lane keeps
+          const float fe = __uint_as_float(v[ce]), fo = __uint_as_float(v[co]);
+          const float mine = odd ? fo : fe;
+          const float give = odd ? fe : fo;
           tot[i] = mine + __shfl_xor_sync(0xffffffffu, give, 1);
         }
-        const int nc = n0 + c0 + 8 * odd;  // first of this lane's 8 columns
-        float b[8];
-        if (p.add_bias && nc < p.R) {
-          const uint4 bv = __ldg(reinterpret_cast<const uint4 *>(bias_row + nc));
-          const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            b[2 * i] = __uint_as_float(bw[i] << 16);
-            b[2 * i + 1] = __uint_as_float(bw[i] & 0xffff0000u);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) b[i] = 0.f;
-        }
         if (MODE == 1) {
+          const int nc = n0 + c0 + 8 * odd;  // first of this lane's 8 columns
+          float b[8];
+          if (nc < p.R) {
+            const uint4 bv = __ldg(reinterpret_cast<const uint4 *>(bias_row + nc));
+            const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              b[2 * i] = __uint_as_float(bw[i] << 16);
+              b[2 * i + 1] = __uint_as_float(bw[i] & 0xffff0000u);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) b[i] = 0.f;
+          }
           float hs[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i)
@@ -252,10 +264,25 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             *reinterpret_cast<uint32_t *>(dst + p.ld_out) = lo4;
           }
         } else {
-          if (tok_ok && nc < p.R) {
-            float4 *dst = reinterpret_cast<float4 *>(p.y_out + static_cast<size_t>(w.row0 + tok) * p.ld_out + nc);
-            dst[0] = make_float4(tot[0] + b[0], tot[1] + b[1], tot[2] + b[2], tot[3] + b[3]);
-            dst[1] = make_float4(tot[4] + b[4], tot[5] + b[5], tot[6] + b[6], tot[7] + b[7]);
+          const int na = n0 + c0 + 4 * odd;  // this lane's columns: na..na+3 and na+8..na+11
+          if (tok_ok && na < p.R) {          // R is a multiple of 32 here, so the whole chunk is inside
+            float b[8];
+            if (p.add_bias) {
+              const uint2 b0 = __ldg(reinterpret_cast<const uint2 *>(bias_row + na));
+              const uint2 b1 = __ldg(reinterpret_cast<const uint2 *>(bias_row + na + 8));
+              const uint32_t bw[4] = {b0.x, b0.y, b1.x, b1.y};
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                b[2 * i] = __uint_as_float(bw[i] << 16);
+                b[2 * i + 1] = __uint_as_float(bw[i] & 0xffff0000u);
+              }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) b[i] = 0.f;
+            }
+            float *dst = p.y_out + static_cast<size_t>(w.row0 + tok) * p.ld_out + na;
+            *reinterpret_cast<float4 *>(dst) = make_float4(tot[0] + b[0], tot[1] + b[1], tot[2] + b[2], tot[3] + b[3]);
+            *reinterpret_cast<float4 *>(dst + 8) = make_float4(tot[4] + b[4], tot[5] + b[5], tot[6] + b[6], tot[7] + b[7]);
           }
         }
       };
