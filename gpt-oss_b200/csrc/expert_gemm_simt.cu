@@ -48,8 +48,8 @@ __device__ __forceinline__ float warp_dot_mxfp4(const uint8_t *codes, const uint
 __global__ void __launch_bounds__(256)
 simt_mlp1_kernel(const uint8_t *__restrict__ codes, int pitch, const uint8_t *__restrict__ scales,
                  const __nv_bfloat16 *__restrict__ bias, const __half *__restrict__ x,
-                 const int *__restrict__ offsets, int E, int H, int R1, __half *__restrict__ h_out, float limit,
-                 float alpha) {
+                 const int *__restrict__ offsets, int E, int H, int R1, __half *__restrict__ h_out, int ld_h,
+                 float limit, float alpha) {
   const int r = blockIdx.x;
   if (r >= offsets[E]) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -64,7 +64,7 @@ simt_mlp1_kernel(const uint8_t *__restrict__ codes, int pitch, const uint8_t *__
   if (lane == 0) {
     g += __bfloat162float(bias[row_g]);
     u += __bfloat162float(bias[row_g + 1]);
-    h_out[static_cast<size_t>(r) * Dl + j] = __float2half_rn(swiglu_clamped(g, u, limit, alpha));
+    h_out[static_cast<size_t>(r) * ld_h + j] = __float2half_rn(swiglu_clamped(g, u, limit, alpha));
   }
 }
 
@@ -87,10 +87,10 @@ simt_mlp2_kernel(const uint8_t *__restrict__ codes, int pitch, const uint8_t *__
 }
 
 void launch_simt_mlp1(const uint8_t *codes, int pitch, const uint8_t *scales_raw, const __nv_bfloat16 *bias,
-                      const __half *x, const int *offsets, int E, int H, int R1, __half *h_out, float limit,
-                      float alpha, int n_rows, cudaStream_t s) {
+                      const __half *x, const int *offsets, int E, int H, int R1, __half *h_out, int ld_h,
+                      float limit, float alpha, int n_rows, cudaStream_t s) {
   dim3 grid(n_rows, (R1 / 2 + 7) / 8);
-  simt_mlp1_kernel<<<grid, 256, 0, s>>>(codes, pitch, scales_raw, bias, x, offsets, E, H, R1, h_out, limit, alpha);
+  simt_mlp1_kernel<<<grid, 256, 0, s>>>(codes, pitch, scales_raw, bias, x, offsets, E, H, R1, h_out, ld_h, limit, alpha);
 }
 
 void launch_simt_mlp2(const uint8_t *codes, int pitch, const uint8_t *scales_raw, const __nv_bfloat16 *bias,

@@ -193,23 +193,23 @@ int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_b
   mark();
   const int add_b2 = c->cfg.tp_rank == 0 ? 1 : 0;
   if (flags & MOE_FWD_SIMT_GEMM) {
-    launch_simt_mlp1(w.w1_codes, c->pitch1, w.w1_scales_raw, w.b1, c->xperm, c->offsets, E, H, c->R1, c->hbuf,
-                     c->cfg.swiglu_limit, c->cfg.swiglu_alpha, P, s);
+    launch_simt_mlp1(w.w1_codes, c->pitch1, w.w1_scales_raw, w.b1, c->xperm, c->offsets, E, H, c->R1,
+                     c->hbuf + c->joff, c->Kw, c->cfg.swiglu_limit, c->cfg.swiglu_alpha, P, s);
     mark();
-    launch_simt_mlp2(w.w2_codes, c->pitch2, w.w2_scales_raw, w.b2, add_b2, c->hbuf, c->offsets, E, c->Dl, H,
+    launch_simt_mlp2(w.w2_codes, c->pitch2, w.w2_scales_raw, w.b2, add_b2, c->hbuf, c->offsets, E, c->Kw, H,
                      c->ybuf, P, s);
   } else {
     GemmArgs a{};
     a.work = c->work1; a.n_work = c->n_work; a.K = H; a.R = c->R1;
     a.n_kchunks = (H + kChunkK - 1) / kChunkK; a.n_ntiles = n_nt1;
     a.sfb = w.w1_scales; a.sfa = c->sfa_x; a.sfa_tile_stride = kSfAtomBytes; a.bias = w.b1; a.add_bias = 1;
-    a.hq_out = c->hq; a.y_out = nullptr; a.ld_out = c->Dl; a.h_exp = c->h_exp;
+    a.hq_out = c->hq + c->joff; a.y_out = nullptr; a.ld_out = c->Kw; a.h_exp = c->h_exp;
     a.limit = c->cfg.swiglu_limit; a.alpha = c->cfg.swiglu_alpha; a.status = c->status;
     launch_expert_gemm_mlp1(w.tm_w1, c->tm_x1, a, c->sm_count, s);
     mark();
     GemmArgs b = a;
-    b.work = c->work2; b.n_work = c->n_work + 1; b.K = c->Dl; b.R = H;
-    b.n_kchunks = (c->Dl + kChunkK - 1) / kChunkK; b.n_ntiles = n_nt2;
+    b.work = c->work2; b.n_work = c->n_work + 1; b.K = c->Kw; b.R = H;
+    b.n_kchunks = (c->Kw + kChunkK - 1) / kChunkK; b.n_ntiles = n_nt2;
     b.sfb = w.w2_scales; b.sfa = c->sfa_h; b.sfa_tile_stride = 0; b.bias = w.b2; b.add_bias = add_b2;
     b.hq_out = nullptr; b.y_out = c->ybuf; b.ld_out = H;
     launch_expert_gemm_mlp2(w.tm_w2, c->tm_x2, b, c->sm_count, s);
@@ -260,11 +260,19 @@ long long moe_launch_count(moe_handle h) { return h ? h->launches : 0; }
 
 int moe_shard_range(int D, int tp_size, int tp_rank, int *start, int *len) {
   if (D <= 0 || D % 32 || tp_size <= 0 || tp_rank < 0 || tp_rank >= tp_size || D / 32 < tp_size) return MOE_ERR_INVALID;
-  const int nblk = D / 32, base = nblk / tp_size, rem = nblk % tp_size;
-  const int l = base + (tp_rank < rem ? 1 : 0);
-  const int s = tp_rank * base + (tp_rank < rem ? tp_rank : rem);
-  if (start) *start = s * 32;
-  if (len) *len = l * 32;
+  int s, l;
+  if (D % tp_size == 0 && (D / tp_size) % 8 == 0) {
+    // the reference's even split (mlp2_shard_input, getp_run.cpp:2495-2501)
+    l = D / tp_size;
+    s = tp_rank * l;
+  } else {
+    // uneven case: distribute whole 32-element scale blocks
+    const int nblk = D / 32, base = nblk / tp_size, rem = nblk % tp_size;
+    l = 32 * (base + (tp_rank < rem ? 1 : 0));
+    s = 32 * (tp_rank * base + (tp_rank < rem ? tp_rank : rem));
+  }
+  if (start) *start = s;
+  if (len) *len = l;
   return MOE_OK;
 }
 
@@ -285,6 +293,11 @@ int moe_create(const moe_config *cfg, moe_handle *out) {
   if (moe_shard_range(c->D, cfg->tp_size, cfg->tp_rank, &c->d0, &c->Dl) != MOE_OK)
     return fail(c, MOE_ERR_INVALID, "intermediate_dim %d cannot be split over %d ranks on 32-element boundaries", c->D, cfg->tp_size);
   c->R1 = 2 * c->Dl;
+  // MLP2 reads the window of whole scale blocks that encloses the shard; the SwiGLU outputs outside the
+  // shard inside that window are never written and stay zero
+  c->k0 = c->d0 / 32 * 32;
+  c->Kw = (c->d0 + c->Dl + 31) / 32 * 32 - c->k0;
+  c->joff = c->d0 - c->k0;
   c->max_rows = cfg->max_rows;
   c->max_pairs = cfg->max_rows * c->K;
   c->layers.resize(c->L);
@@ -310,7 +323,7 @@ int moe_create(const moe_config *cfg, moe_handle *out) {
   if ((rc = dev_alloc(c, &c->pair_row, T * c->K))) return rc;
   if ((rc = dev_alloc(c, &c->row_token, P))) return rc;
   if ((rc = dev_alloc(c, &c->xperm, P * c->H))) return rc;
-  if ((rc = dev_alloc(c, &c->hbuf, P * c->Dl))) return rc;
+  if ((rc = dev_alloc(c, &c->hbuf, P * c->Kw))) return rc;
   if ((rc = dev_alloc(c, &c->ybuf, P * c->H))) return rc;
   if ((rc = dev_alloc(c, &c->out_f32, T * c->H))) return rc;
   if ((rc = dev_alloc(c, &c->out_bf16, T * c->H))) return rc;
@@ -340,12 +353,12 @@ int moe_create(const moe_config *cfg, moe_handle *out) {
   }
   const size_t tile_rows = static_cast<size_t>(c->max_tiles) * kTileM;
   if ((rc = dev_alloc(c, &c->xq, tile_rows * c->H))) return rc;
-  if ((rc = dev_alloc(c, &c->hq, tile_rows * c->Dl))) return rc;
+  if ((rc = dev_alloc(c, &c->hq, tile_rows * c->Kw))) return rc;
   if ((rc = dev_alloc(c, &c->sfa_x, static_cast<size_t>(c->max_tiles) * kSfAtomBytes))) return rc;
   if ((rc = dev_alloc(c, &c->sfa_h, static_cast<size_t>(kSfAtomBytes)))) return rc;
   if ((rc = dev_alloc(c, &c->tile_base, static_cast<size_t>(c->E) + 1))) return rc;
   CU_TRY(c, cudaMemset(c->xq, 0, tile_rows * c->H));
-  CU_TRY(c, cudaMemset(c->hq, 0, tile_rows * c->Dl));
+  CU_TRY(c, cudaMemset(c->hq, 0, tile_rows * c->Kw));
   CU_TRY(c, cudaMemset(c->sfa_x, 127, static_cast<size_t>(c->max_tiles) * kSfAtomBytes));
   {
     uint8_t atom[kSfAtomBytes];
@@ -362,9 +375,9 @@ int moe_create(const moe_config *cfg, moe_handle *out) {
   CU_TRY(c, cudaMemset(c->n_work, 0, 2 * sizeof(int)));
   // Rows past the current batch are read (and discarded) by token tiles that overhang; keep them finite.
   CU_TRY(c, cudaMemset(c->xperm, 0, P * c->H * sizeof(__half)));
-  CU_TRY(c, cudaMemset(c->hbuf, 0, P * c->Dl * sizeof(__half)));
+  CU_TRY(c, cudaMemset(c->hbuf, 0, P * c->Kw * sizeof(__half)));
   if ((rc = make_act_map(c, &c->tm_x1, c->xq, static_cast<int>(tile_rows), c->H))) return rc;
-  if ((rc = make_act_map(c, &c->tm_x2, c->hq, static_cast<int>(tile_rows), c->Dl))) return rc;
+  if ((rc = make_act_map(c, &c->tm_x2, c->hq, static_cast<int>(tile_rows), c->Kw))) return rc;
   return MOE_OK;
 }
 
@@ -396,13 +409,13 @@ int moe_load_layer(moe_handle c, int layer, const uint8_t *w1_codes, const uint8
   if (layer < 0 || layer >= c->L || !w1_codes || !w1_scales || !b1 || !w2_codes || !w2_scales || !b2 || !router_w || !router_b)
     return fail(c, MOE_ERR_INVALID, "moe_load_layer: bad layer index or null tensor");
   CU_TRY(c, cudaSetDevice(c->cfg.device));
-  const int E = c->E, H = c->H, D = c->D, Dl = c->Dl, d0 = c->d0, R1 = c->R1;
+  const int E = c->E, H = c->H, D = c->D, d0 = c->d0, R1 = c->R1, k0 = c->k0, Kw = c->Kw;
   LayerWeights &w = c->layers[layer];
   free_layer(w);
 
   // ---- this rank's shard, still in the reference layout -------------------
   // MLP1: rows [2*d0, 2*(d0+Dl)) of every expert (gate/up pairs stay adjacent);
-  // MLP2: columns [d0, d0+Dl).  Scale blocks (32 along the input dim) are never cut.
+  // MLP2: columns [k0, k0+Kw), the whole scale blocks that enclose the shard [d0, d0+Dl).
   // Row pitch of the packed codes: K/2 bytes rounded up to 32 (a TMA requirement of the 4-bit
   // element type); pad bytes are zero codes.
   const size_t w1_row = H / 2, s1_row = H / 32, p1 = (w1_row + 31) / 32 * 32;
@@ -415,11 +428,11 @@ int moe_load_layer(moe_handle c, int layer, const uint8_t *w1_codes, const uint8
     memcpy(&s1[static_cast<size_t>(e) * R1 * s1_row], w1_scales + src_row0 * s1_row, static_cast<size_t>(R1) * s1_row);
     memcpy(&bb1[static_cast<size_t>(e) * R1], b1 + src_row0, static_cast<size_t>(R1) * 2);
   }
-  const size_t w2_row = Dl / 2, s2_row = Dl / 32, p2 = (w2_row + 31) / 32 * 32;
+  const size_t w2_row = Kw / 2, s2_row = Kw / 32, p2 = (w2_row + 31) / 32 * 32;
   std::vector<uint8_t> c2(static_cast<size_t>(E) * H * p2, 0), s2(static_cast<size_t>(E) * H * s2_row);
   for (size_t r = 0; r < static_cast<size_t>(E) * H; ++r) {
-    memcpy(&c2[r * p2], w2_codes + r * (D / 2) + d0 / 2, w2_row);
-    memcpy(&s2[r * s2_row], w2_scales + r * (D / 32) + d0 / 32, s2_row);
+    memcpy(&c2[r * p2], w2_codes + r * (D / 2) + k0 / 2, w2_row);
+    memcpy(&s2[r * s2_row], w2_scales + r * (D / 32) + k0 / 32, s2_row);
   }
   c->pitch1 = static_cast<int>(p1);
   c->pitch2 = static_cast<int>(p2);
@@ -429,10 +442,10 @@ int moe_load_layer(moe_handle c, int layer, const uint8_t *w1_codes, const uint8
       if (b == 0xFF) return fail(c, MOE_ERR_SCALE_RANGE, "layer %d: E8M0 scale byte 0xFF (NaN)", layer);
 
   const int n_nt1 = (R1 + kTileN - 1) / kTileN, n_kc1 = (H + kChunkK - 1) / kChunkK;
-  const int n_nt2 = (H + kTileN - 1) / kTileN, n_kc2 = (Dl + kChunkK - 1) / kChunkK;
+  const int n_nt2 = (H + kTileN - 1) / kTileN, n_kc2 = (Kw + kChunkK - 1) / kChunkK;
   std::vector<uint8_t> t1, t2;
   tile_scales(s1.data(), E, R1, H / 32, n_nt1, n_kc1, t1);
-  tile_scales(s2.data(), E, H, Dl / 32, n_nt2, n_kc2, t2);
+  tile_scales(s2.data(), E, H, Kw / 32, n_nt2, n_kc2, t2);
 
   // router weight as three bf16 planes whose sum is the fp32 value exactly
   std::vector<uint16_t> w3(static_cast<size_t>(3) * E * H);
@@ -470,7 +483,7 @@ int moe_load_layer(moe_handle c, int layer, const uint8_t *w1_codes, const uint8
   CU_TRY(c, cudaMemcpy(w.router_w3, w3.data(), w3.size() * 2, cudaMemcpyHostToDevice));
   CU_TRY(c, cudaMemcpy(w.router_b, router_b, static_cast<size_t>(E) * 4, cudaMemcpyHostToDevice));
   if ((rc = make_weight_map(c, &w.tm_w1, w.w1_codes, E, R1, H, c->pitch1))) return rc;
-  if ((rc = make_weight_map(c, &w.tm_w2, w.w2_codes, E, H, Dl, c->pitch2))) return rc;
+  if ((rc = make_weight_map(c, &w.tm_w2, w.w2_codes, E, H, Kw, c->pitch2))) return rc;
   w.loaded = true;
   return MOE_OK;
 }

@@ -100,6 +100,8 @@ struct moe_ctx {
   int H, D, E, K, L;
   int d0, Dl;     // this rank's slice of the intermediate dimension
   int R1;         // 2*Dl
+  int k0, Kw;     // MLP2 reads intermediate columns [k0, k0+Kw): the whole scale blocks around the shard
+  int joff;       // d0 - k0: column of the shard's first SwiGLU output inside that window
   int max_rows, max_pairs;
   int sm_count;
   cudaStream_t stream = nullptr;  // used by moe_forward_host
@@ -190,8 +192,8 @@ void launch_tp_reduce_scatter_pull(const TpPeers &peers, int tp, int rank, int r
 
 // expert_gemm_simt.cu (validation path)
 void launch_simt_mlp1(const uint8_t *codes, int pitch, const uint8_t *scales_raw, const __nv_bfloat16 *bias,
-                      const __half *x, const int *offsets, int E, int H, int R1, __half *h_out, float limit,
-                      float alpha, int n_rows, cudaStream_t s);
+                      const __half *x, const int *offsets, int E, int H, int R1, __half *h_out, int ld_h,
+                      float limit, float alpha, int n_rows, cudaStream_t s);
 void launch_simt_mlp2(const uint8_t *codes, int pitch, const uint8_t *scales_raw, const __nv_bfloat16 *bias,
                       int add_bias, const __half *h, const int *offsets, int E, int Dl, int H, float *y_out,
                       int n_rows, cudaStream_t s);

@@ -69,14 +69,16 @@ int moe_destroy(moe_handle h);
  *   w2_codes  [E, H, D/2], w2_scales [E, H, D/32], b2 [E, H] bf16
  *   router_w  [E, H] fp32, router_b [E] fp32
  * With tp_size > 1 the rank's shard (mlp1_shard / mlp2_shard_input,
- * getp_run.cpp:2488-2501, here on 32-element boundaries so that scale blocks
- * are never split or re-quantised) is cut out inside. */
+ * getp_run.cpp:2488-2501) is cut out inside.  Nothing is re-quantised: where a
+ * shard boundary falls inside a 32-element scale block, MLP2 keeps the whole
+ * blocks around its shard and the activations outside the shard are zero. */
 int moe_load_layer(moe_handle h, int layer, const uint8_t *w1_codes, const uint8_t *w1_scales,
                    const uint16_t *b1, const uint8_t *w2_codes, const uint8_t *w2_scales,
                    const uint16_t *b2, const float *router_w, const float *router_b);
 
-/* The intermediate range [start, start+len) a rank owns; mirrors
- * mlp2_shard_input (getp_run.cpp:2495-2501) with 32-aligned boundaries. */
+/* The intermediate range [start, start+len) a rank owns: the even split of
+ * mlp2_shard_input (getp_run.cpp:2495-2501) when D / tp_size is a whole multiple
+ * of 8, otherwise whole 32-element blocks dealt out as evenly as possible. */
 int moe_shard_range(int intermediate_dim, int tp_size, int tp_rank, int *start, int *len);
 
 /* moe_forward.flags */

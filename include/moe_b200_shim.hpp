@@ -38,8 +38,8 @@ inline void tp_init(TPGroup &tp, int world_size, int world_rank, int tp_size) {
 }
 inline void tp_free(TPGroup &) {}  // getp-csrc/nccl.hpp:92-98: nothing to release here
 
-// getp-csrc/getp_run.cpp:2488-2501.  The shard boundaries fall on multiples of 32 so that MXFP4 scale
-// blocks are never cut (the reference re-quantises each shard instead).
+// getp-csrc/getp_run.cpp:2488-2501: the same even split.  The library never re-quantises a shard (the
+// reference does): MLP2 keeps the whole scale blocks around its shard.
 inline void mlp2_shard_input(int D, int tp_size, int r, int &i_start, int &i_len) {
   if (moe_shard_range(D, tp_size, r, &i_start, &i_len) != MOE_OK) { i_start = 0; i_len = 0; }
 }

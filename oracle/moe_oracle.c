@@ -144,7 +144,8 @@ static inline float swiglu_ref(float val, float up_val, float limit) {
  * same operations in the same order: out[t] receives its experts' terms in
  * ascending expert index.
  * d0/d1 restrict the intermediate range to [d0,d1) (a tensor-parallel shard,
- * getp-csrc/getp_run.cpp:2488-2501); add_b2 = 0 leaves the MLP2 bias out so
+ * getp-csrc/getp_run.cpp:2488-2501; it need not fall on scale-block boundaries:
+ * the enclosing whole blocks of an MLP2 row are decoded and the shard cut out); add_b2 = 0 leaves the MLP2 bias out so
  * that shard partials can be summed.  d0=0, d1=D, add_b2=1 is the full block.
  */
 int oracle_moe_layer_shard(const float *t, int T, int H, int D, int E, int K,
@@ -154,7 +155,7 @@ int oracle_moe_layer_shard(const float *t, int T, int H, int D, int E, int K,
                            const float *br, int d0, int d1, int add_b2,
                            float *logits, int *topk_i, float *topk_v,
                            float *out) {
-  if (H % 32 || D % 32 || d0 % 32 || d1 % 32 || d0 < 0 || d1 > D || d0 >= d1)
+  if (H % 32 || D % 32 || d0 < 0 || d1 > D || d0 >= d1)
     return -1;
   oracle_router_logits(t, wr, br, T, H, E, logits);
   oracle_topk_softmax(logits, T, E, K, topk_i, topk_v);
@@ -214,13 +215,14 @@ int oracle_moe_layer_shard(const float *t, int T, int H, int D, int E, int K,
     const float *bb2 = b2 + (size_t)e * H;
 #pragma omp parallel
     {
-      float *row = (float *)malloc((size_t)Dl * sizeof(float));
+      const int k0 = d0 / 32 * 32, k1 = (d1 + 31) / 32 * 32;
+      float *row = (float *)malloc((size_t)(k1 - k0) * sizeof(float));
 #pragma omp for schedule(static)
       for (int i = 0; i < H; ++i) {
-        oracle_mxfp4_dequant_span(c2 + (size_t)i * (D / 2) + d0 / 2,
-                                  s2 + (size_t)i * (D / 32) + d0 / 32, Dl, row);
+        oracle_mxfp4_dequant_span(c2 + (size_t)i * (D / 2) + k0 / 2,
+                                  s2 + (size_t)i * (D / 32) + k0 / 32, k1 - k0, row);
         for (int r = 0; r < n; ++r) {
-          float v = dot_f32_acc64(row, gu + (size_t)r * Dl, Dl);
+          float v = dot_f32_acc64(row + (d0 - k0), gu + (size_t)r * Dl, Dl);
           if (add_b2)
             v += bb2[i];
           y[(size_t)r * H + i] = v;

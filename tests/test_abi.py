@@ -24,18 +24,22 @@ def test_library_exports_every_declared_symbol(pkg):
     assert set(pkg.EXPORTS) <= set(names)
 
 
-def test_shard_ranges_are_32_aligned_and_cover(pkg):
-    for D, tp in [(2880, 1), (2880, 2), (2880, 4), (2880, 8), (96, 3), (64, 2)]:
+def test_shard_ranges_cover_and_follow_the_reference_split(pkg):
+    for D, tp in [(2880, 1), (2880, 2), (2880, 4), (2880, 8), (96, 3), (64, 2), (320, 4), (160, 3)]:
         pos = 0
         lens = []
         for r in range(tp):
             s, n = pkg.shard_range(D, tp, r)
-            assert s == pos and s % 32 == 0 and n % 32 == 0 and n > 0
+            assert s == pos and n > 0 and n % 8 == 0
             pos += n
             lens.append(n)
         assert pos == D
         assert max(lens) - min(lens) <= 32
-    assert [pkg.shard_range(2880, 4, r)[1] for r in range(4)] == [736, 736, 704, 704]
+    # even split as mlp2_shard_input of the reference whenever it yields whole gate/up row groups
+    assert [pkg.shard_range(2880, 4, r) for r in range(4)] == [(0, 720), (720, 720), (1440, 720), (2160, 720)]
+    assert [pkg.shard_range(2880, 8, r)[1] for r in range(8)] == [360] * 8
+    # otherwise whole 32-element scale blocks are dealt out
+    assert [pkg.shard_range(160, 3, r) for r in range(3)] == [(0, 64), (64, 64), (128, 32)]
     with pytest.raises(pkg.MoeError):
         pkg.shard_range(2880, 4, 4)
     with pytest.raises(pkg.MoeError):
@@ -83,8 +87,8 @@ def test_cpp_shim_compiles_and_links(tmp_path):
     src.write_text('#include "moe_b200_shim.hpp"\n'
                    'int main() { TPGroup tp; tp_init(tp, 8, 5, 4); int s, n; mlp1_shard(5760, 4, 1, s, n);\n'
                    '  int a, b; mlp2_shard_input(2880, 4, 3, a, b);\n'
-                   '  return (tp.group_id == 1 && tp.rank_in_group == 1 && tp.group_devs[3] == 7 && s == 1472 && n == 1472\n'
-                   '          && a == 2176 && b == 704) ? 0 : 1; }\n')
+                   '  return (tp.group_id == 1 && tp.rank_in_group == 1 && tp.group_devs[3] == 7 && s == 1440 && n == 1440\n'
+                   '          && a == 2160 && b == 720) ? 0 : 1; }\n')
     gxx = shutil.which("g++")
     if gxx is None or not os.path.exists("/usr/local/cuda/include/cuda_runtime.h"):
         pytest.skip("no host compiler or CUDA headers")

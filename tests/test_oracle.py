@@ -62,17 +62,18 @@ def test_port_matches_reference_live(E, H, D, T, seed, synth, port):
 
 
 def test_shard_partials_sum_to_full_block(synth, port):
-    """Tensor-parallel split of the intermediate dimension (32-aligned shards,
-    MLP2 bias added once): partial outputs add up to the unsharded block."""
+    """Tensor-parallel split of the intermediate dimension (shards need not fall on
+    scale-block boundaries; MLP2 bias added once): partial outputs add up to the
+    unsharded block."""
     layer = synth.make_layer(8, 64, 96, seed=3)
     tokens = synth.make_tokens(12, 64, seed=4)
     _, idx, w, full = port.moe_layer(layer, tokens)
     parts = []
-    for r, (d0, d1) in enumerate([(0, 32), (32, 96)]):
+    for r, (d0, d1) in enumerate([(0, 24), (24, 72), (72, 96)]):
         _, i2, w2, o = port.moe_layer(layer, tokens, shard=(d0, d1), add_b2=(r == 0))
         assert np.array_equal(i2, idx) and np.array_equal(w2, w)
         parts.append(o.astype(np.float64))
-    np.testing.assert_allclose(parts[0] + parts[1], full, rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(parts[0] + parts[1] + parts[2], full, rtol=1e-5, atol=1e-5)
 
 
 def test_mxfp4_decode(synth, port):
