@@ -587,7 +587,7 @@ int moe_get_debug(moe_handle c, int which, void *dst, size_t bytes) {
     case MOE_DBG_ROW_TOKEN: src = c->row_token; have = T * c->K * 4; break;
     case MOE_DBG_OUT_F32: src = c->out_f32; have = T * c->H * 4; break;
     case MOE_DBG_STATUS: src = c->status; have = 4096 * 4; break;
-    case MOE_DBG_GATHER: src = c->t_in; have = T * c->H * 2; break;
+    case MOE_DBG_GATHER: src = c->t_in; have = static_cast<size_t>(c->max_rows) * c->H * 2; break;
     case MOE_DBG_YBUF: src = c->ybuf; have = T * c->K * c->H * 4; break;
     default: return fail(c, MOE_ERR_INVALID, "moe_get_debug: unknown item %d", which);
   }

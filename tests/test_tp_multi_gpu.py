@@ -50,3 +50,42 @@ def test_tp_forward_single_rank_group(pkg, synth, port):
         assert err.mean() / np.abs(ref).mean() <= 5e-3 and err.max() <= 2e-2 * max(1.0, float(np.sqrt((ref ** 2).mean())))
     finally:
         blk.close()
+
+
+def test_peer_that_never_arrives_is_reported_not_hung(pkg, synth):
+    """Failure detection without a fault: a rank waits for a peer flag that nothing sets.  The
+    device-side wait is bounded (about a second); it records a status bit, the kernel returns,
+    the host call reports MOE_ERR_TIMEOUT, and the context keeps working.  (The reference's
+    tp_group_barrier spins forever in that situation, getp-csrc/nccl.hpp:133-135.)
+    Both handles live on one GPU; only rank 0 ever launches, so no two kernels wait on each other."""
+    import numpy as np
+    import torch
+    E, H, D, T = 8, 128, 128, 16
+    layer = synth.make_layer(E, H, D, seed=71)
+    r0 = pkg.MoeBlock(H, D, E, max_rows=2 * T, tp_size=2, tp_rank=0)
+    r1 = pkg.MoeBlock(H, D, E, max_rows=2 * T, tp_size=2, tp_rank=1)   # the silent peer
+    try:
+        r0.load_layer(0, layer)
+        lib = pkg.lib()
+        import ctypes as C
+        for which in range(pkg.TP_N_BUFS):
+            r0._check(lib.moe_tp_attach_ptr(r0.h, which, 1, C.c_void_p(r1.tp_buffer(which)), 0))
+        rows = torch.from_numpy(synth.make_tokens(T, H, seed=72).view(np.int16)).cuda()
+        r0.tp_allgather(rows.data_ptr(), T, torch.cuda.current_stream().cuda_stream)
+        with pytest.raises(pkg.MoeError) as ei:
+            r0.synchronize()
+        assert ei.value.code == 4                      # MOE_ERR_TIMEOUT
+        assert "0x80" in str(ei.value)                 # the peer-wait bit of the status word
+        # the push itself happened: the silent peer's gather buffer holds rank 0's rows in slot 0
+        r1.rows = T
+        got = r1.debug(pkg.DBG_GATHER)
+        assert np.array_equal(got, rows.cpu().numpy().view(np.uint16))
+        # and the context is still usable: a plain forward on a fresh single-rank handle works
+        solo = pkg.MoeBlock(H, D, E, max_rows=T)
+        solo.load_layer(0, layer)
+        out = solo.forward_host(0, rows.cpu().numpy().view(np.uint16))
+        assert np.isfinite(synth.bf16_bits_to_f32(out)).all()
+        solo.close()
+    finally:
+        r0.close()
+        r1.close()
