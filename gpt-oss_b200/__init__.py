@@ -27,13 +27,13 @@ FWD_SIMT_GEMM = 1
 FWD_PARTIAL_F32 = 2
 
 DBG_LOGITS, DBG_TOPK_IDX, DBG_TOPK_W, DBG_COUNTS, DBG_OFFSETS, DBG_PAIR_ROW, DBG_ROW_TOKEN, DBG_OUT_F32, \
-    DBG_STATUS, DBG_HBUF, DBG_YBUF, DBG_GATHER = range(12)
+    DBG_STATUS, DBG_HBUF, DBG_YBUF, DBG_GATHER, DBG_TNORM = range(13)
 
 EXPORTS = [
     "moe_create", "moe_destroy", "moe_load_layer", "moe_shard_range", "moe_forward", "moe_forward_host",
     "moe_synchronize", "moe_host_alloc", "moe_host_free", "moe_route_topk", "moe_get_debug",
     "moe_last_error", "moe_strerror", "moe_launch_count", "moe_profile_enable", "moe_profile_collect",
-    "moe_route_static", "moe_tp_export", "moe_tp_attach_ipc", "moe_tp_buffer", "moe_tp_attach_ptr",
+    "moe_route_static", "moe_block", "moe_tp_export", "moe_tp_attach_ipc", "moe_tp_buffer", "moe_tp_attach_ptr",
     "moe_tp_forward", "moe_tp_forward_host", "moe_tp_allgather", "moe_tp_reduce_scatter",
 ]
 TP_BUF_GATHER, TP_BUF_PARTIAL, TP_BUF_FLAGS, TP_BUF_TOPK_IDX, TP_BUF_TOPK_W = range(5)
@@ -94,6 +94,7 @@ def lib() -> C.CDLL:
         L.moe_tp_forward_host.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_uint]
         L.moe_tp_allgather.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
         L.moe_tp_reduce_scatter.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
+        L.moe_block.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_uint, C.c_void_p]
         L.moe_profile_enable.argtypes = [C.c_void_p, C.c_int]
         L.moe_profile_collect.argtypes = [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_int)]
         _lib = L
@@ -182,6 +183,12 @@ class MoeBlock:
                                        C.c_void_p(stream)))
         self.rows = rows
 
+    def block(self, layer: int, x_ptr: int, rms_w_ptr: int, rows_local: int, flags: int = 0, stream: int = 0):
+        """x <- x + MoE(rmsnorm(x) * w), in place, device pointers (the reference's moe_gpu form)."""
+        self._check(self.L.moe_block(self.h, layer, C.c_void_p(x_ptr), C.c_void_p(rms_w_ptr), rows_local, flags,
+                                     C.c_void_p(stream)))
+        self.rows = rows_local * self.cfg.tp_size
+
     def synchronize(self):
         self._check(self.L.moe_synchronize(self.h))
 
@@ -242,7 +249,7 @@ class MoeBlock:
             DBG_COUNTS: ((E,), np.int32), DBG_OFFSETS: ((E + 1,), np.int32), DBG_PAIR_ROW: ((T, K), np.int32),
             DBG_ROW_TOKEN: ((T * K,), np.int32), DBG_OUT_F32: ((T, H), np.float32),
             DBG_STATUS: ((1,), np.uint32), DBG_YBUF: ((T * K, H), np.float32),
-            DBG_GATHER: ((T, H), np.uint16)}[which]
+            DBG_GATHER: ((T, H), np.uint16), DBG_TNORM: ((T // self.cfg.tp_size, H), np.uint16)}[which]
         out = np.empty(shape, dtype=dt)
         self._check(self.L.moe_get_debug(self.h, which, out.ctypes.data_as(C.c_void_p), out.nbytes))
         return out

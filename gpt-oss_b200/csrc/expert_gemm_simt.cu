@@ -18,12 +18,13 @@ __device__ __forceinline__ int expert_of_row(const int *offsets, int E, int r) {
   return lo;
 }
 
-// dot of one weight row (packed codes + raw row-major scales) with an fp16 row
+// dot of one weight row (packed codes inside the 16 KB weight tiles: `codes` points at the row's 64 bytes in the
+// first tile of its row block, the next 128 k follow one tile further; raw row-major scales) with an fp16 row
 __device__ __forceinline__ float warp_dot_mxfp4(const uint8_t *codes, const uint8_t *scales, const __half *x,
                                                 int K, int lane) {
   float acc = 0.f;
   for (int b = lane; b < K / 32; b += 32) {
-    const uint4 c = *reinterpret_cast<const uint4 *>(codes + b * 16);
+    const uint4 c = *reinterpret_cast<const uint4 *>(codes + static_cast<size_t>(b >> 2) * kWTileStride + (b & 3) * 16);
     uint32_t w[16];
     sm100::dequant_block32(c, sm100::e8m0_to_f16x2(scales[b]), w);
     const uint4 *xp = reinterpret_cast<const uint4 *>(x + b * 32);
@@ -45,8 +46,14 @@ __device__ __forceinline__ float warp_dot_mxfp4(const uint8_t *codes, const uint
   return acc;
 }
 
+// the 64 code bytes of row `row` of expert e's [R x K] matrix in the first tile of the row's block
+__device__ __forceinline__ const uint8_t *tile_row(const uint8_t *w_tiles, int e, int row, int R, int K) {
+  const int n_nt = (R + kTileN - 1) / kTileN, n_kc = (K + kChunkK - 1) / kChunkK;
+  return w_tiles + (static_cast<size_t>(e) * n_nt + row / kTileN) * n_kc * kWTileStride + (row % kTileN) * (kChunkK / 2);
+}
+
 __global__ void __launch_bounds__(256)
-simt_mlp1_kernel(const uint8_t *__restrict__ codes, int pitch, const uint8_t *__restrict__ scales,
+simt_mlp1_kernel(const uint8_t *__restrict__ w_tiles, const uint8_t *__restrict__ scales,
                  const __nv_bfloat16 *__restrict__ bias, const __half *__restrict__ x,
                  const int *__restrict__ offsets, int E, int H, int R1, __half *__restrict__ h_out, int ld_h,
                  float limit, float alpha) {
@@ -59,8 +66,8 @@ simt_mlp1_kernel(const uint8_t *__restrict__ codes, int pitch, const uint8_t *__
   const int e = expert_of_row(offsets, E, r);
   const size_t row_g = static_cast<size_t>(e) * R1 + 2 * j;
   const __half *xr = x + static_cast<size_t>(r) * H;
-  float g = warp_dot_mxfp4(codes + row_g * pitch, scales + row_g * (H / 32), xr, H, lane);
-  float u = warp_dot_mxfp4(codes + (row_g + 1) * pitch, scales + (row_g + 1) * (H / 32), xr, H, lane);
+  float g = warp_dot_mxfp4(tile_row(w_tiles, e, 2 * j, R1, H), scales + row_g * (H / 32), xr, H, lane);
+  float u = warp_dot_mxfp4(tile_row(w_tiles, e, 2 * j + 1, R1, H), scales + (row_g + 1) * (H / 32), xr, H, lane);
   if (lane == 0) {
     g += __bfloat162float(bias[row_g]);
     u += __bfloat162float(bias[row_g + 1]);
@@ -69,7 +76,7 @@ simt_mlp1_kernel(const uint8_t *__restrict__ codes, int pitch, const uint8_t *__
 }
 
 __global__ void __launch_bounds__(256)
-simt_mlp2_kernel(const uint8_t *__restrict__ codes, int pitch, const uint8_t *__restrict__ scales,
+simt_mlp2_kernel(const uint8_t *__restrict__ w_tiles, const uint8_t *__restrict__ scales,
                  const __nv_bfloat16 *__restrict__ bias, int add_bias, const __half *__restrict__ h,
                  const int *__restrict__ offsets, int E, int Dl, int H, float *__restrict__ y_out) {
   const int r = blockIdx.x;
@@ -79,25 +86,25 @@ simt_mlp2_kernel(const uint8_t *__restrict__ codes, int pitch, const uint8_t *__
   if (i >= H) return;
   const int e = expert_of_row(offsets, E, r);
   const size_t row = static_cast<size_t>(e) * H + i;
-  float v = warp_dot_mxfp4(codes + row * pitch, scales + row * (Dl / 32), h + static_cast<size_t>(r) * Dl, Dl, lane);
+  float v = warp_dot_mxfp4(tile_row(w_tiles, e, i, H, Dl), scales + row * (Dl / 32), h + static_cast<size_t>(r) * Dl, Dl, lane);
   if (lane == 0) {
     if (add_bias) v += __bfloat162float(bias[row]);
     y_out[static_cast<size_t>(r) * H + i] = v;
   }
 }
 
-void launch_simt_mlp1(const uint8_t *codes, int pitch, const uint8_t *scales_raw, const __nv_bfloat16 *bias,
+void launch_simt_mlp1(const uint8_t *w_tiles, const uint8_t *scales_raw, const __nv_bfloat16 *bias,
                       const __half *x, const int *offsets, int E, int H, int R1, __half *h_out, int ld_h,
                       float limit, float alpha, int n_rows, cudaStream_t s) {
   dim3 grid(n_rows, (R1 / 2 + 7) / 8);
-  simt_mlp1_kernel<<<grid, 256, 0, s>>>(codes, pitch, scales_raw, bias, x, offsets, E, H, R1, h_out, ld_h, limit, alpha);
+  simt_mlp1_kernel<<<grid, 256, 0, s>>>(w_tiles, scales_raw, bias, x, offsets, E, H, R1, h_out, ld_h, limit, alpha);
 }
 
-void launch_simt_mlp2(const uint8_t *codes, int pitch, const uint8_t *scales_raw, const __nv_bfloat16 *bias,
+void launch_simt_mlp2(const uint8_t *w_tiles, const uint8_t *scales_raw, const __nv_bfloat16 *bias,
                       int add_bias, const __half *h, const int *offsets, int E, int Dl, int H, float *y_out,
                       int n_rows, cudaStream_t s) {
   dim3 grid(n_rows, (H + 7) / 8);
-  simt_mlp2_kernel<<<grid, 256, 0, s>>>(codes, pitch, scales_raw, bias, add_bias, h, offsets, E, Dl, H, y_out);
+  simt_mlp2_kernel<<<grid, 256, 0, s>>>(w_tiles, scales_raw, bias, add_bias, h, offsets, E, Dl, H, y_out);
 }
 
 }  // namespace moe

@@ -128,9 +128,10 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       bool ok = true;
       WorkItem w_next = {};
       if (static_cast<int>(blockIdx.x) < n_work) w_next = p.work[blockIdx.x];
-      for (int wi = blockIdx.x; ok && wi < n_work; wi += gridDim.x, ++item) {
+      for (int wi = blockIdx.x; ok && wi < n_work; wi += gridDim.x) {
         const WorkItem w = w_next;
         if (wi + static_cast<int>(gridDim.x) < n_work) w_next = p.work[wi + gridDim.x];
+       for (int blk = 0; ok && blk < w.nblk; ++blk, ++item) {
         // activation scale atom of this token tile, through its own ring so that the producer never waits
         // for an epilogue; a slot is free once the MMAs of the item that used it are done
         const uint32_t q = item % kSfaSlots;
@@ -138,17 +139,18 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         mbar_arrive_expect_tx(sfa_full_bar(q), kSfAtomBytes);
         bulk_load(smem_base + kSfaOff + q * kSfAtomBytes, p.sfa + static_cast<size_t>(w.tile) * p.sfa_tile_stride,
                   kSfAtomBytes, sfa_full_bar(q));
-        const uint8_t *sfb_src = p.sfb + (static_cast<size_t>(w.expert) * p.n_ntiles + w.ntile) * nkc * kSfbChunkBytes;
+        const uint32_t tile0 = (static_cast<uint32_t>(w.expert) * p.n_ntiles + w.ntile + blk) * nkc;
         for (int kc = 0; kc < nkc; ++kc, ++it) {
           const int s = it % kStages;
           if (!mbar_wait(empty_bar(s), ((it / kStages) & 1u) ^ 1u, abort_flag, p.status, ST_WAIT_EMPTY)) { ok = false; break; }
           const uint32_t stage = smem_base + s * kStageBytes;
           mbar_arrive_expect_tx(full_bar(s), kABytes + kWLoadBytes + kSfbChunkBytes);
           tma_load_2d(stage, &tm_x, kc * kChunkK, w.tile * kTileM, full_bar(s));
-          tma_load_3d(stage + kABytes, &tm_w, kc * kChunkK, w.ntile * kTileN, w.expert, full_bar(s));
-          bulk_load(stage + kABytes + kWBytes, sfb_src + static_cast<size_t>(kc) * kSfbChunkBytes, kSfbChunkBytes,
-                    full_bar(s));
+          tma_load_3d(stage + kABytes, &tm_w, 0, 0, static_cast<int>(tile0 + kc), full_bar(s));
+          bulk_load(stage + kABytes + kWBytes, p.w_tiles + static_cast<size_t>(tile0 + kc) * kWTileStride + kWTileCodes,
+                    kSfbChunkBytes, full_bar(s));
         }
+       }
       }
       if (!ok) {  // give copies in flight time to land before the CTA's shared memory is released
         for (int i = 0; i < 2000; ++i) __nanosleep(1000);
@@ -159,7 +161,14 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     if (lane == 0) {
       uint32_t it = 0, item = 0;
       bool ok = true;
-      for (int wi = blockIdx.x; ok && wi < n_work; wi += gridDim.x, ++item) {
+      const uint64_t desc_fixed = smem_desc_sw128(0);
+      const int full_chunks = K / kChunkK, tail_steps = (K % kChunkK) / 32;
+      uint32_t nblk_next = 0;
+      if (static_cast<int>(blockIdx.x) < n_work) nblk_next = p.work[blockIdx.x].nblk;
+      for (int wi = blockIdx.x; ok && wi < n_work; wi += gridDim.x) {
+       const uint32_t nblk = nblk_next;
+       if (wi + static_cast<int>(gridDim.x) < n_work) nblk_next = p.work[wi + gridDim.x].nblk;
+       for (uint32_t blk = 0; ok && blk < nblk; ++blk, ++item) {
         const uint32_t d = item & 1u;
         if (!mbar_wait(dempty_bar(d), ((item >> 1) & 1u) ^ 1u, abort_flag, p.status, ST_WAIT_DEMPTY)) { ok = false; break; }
         const uint32_t q = item % kSfaSlots;
@@ -176,11 +185,16 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
           const uint32_t sfb_t = tmem_base + kSfbCol0 + 8 * (it & 1u);
           tmem_cp_sf_atom(sfb_t, stage + kABytes + kWBytes);
           tmem_cp_sf_atom(sfb_t + 4, stage + kABytes + kWBytes + kSfAtomBytes);
-          const int ksteps = min(4, (K - kc * kChunkK) / 32);
-          for (int kb = 0; kb < ksteps; ++kb) {
-            const uint64_t adesc = smem_desc_sw128(stage + kb * 32);
-            const uint64_t bdesc = smem_desc_sw128(stage + kABytes + kb * 32);
-            mma_mxf8f6f4_ss(d_addr, adesc, bdesc, idesc_mxf8f6f4_m128(kTileN, kb), (kc | kb) != 0, sfa_t, sfb_t);
+          const uint64_t adesc = desc_fixed | (stage >> 4), bdesc = desc_fixed | ((stage + kABytes) >> 4);
+          if (kc < full_chunks) {
+            mma_mxf8f6f4_ss(d_addr, adesc, bdesc, idesc_mxf8f6f4_m128(kTileN, 0), kc != 0, sfa_t, sfb_t);
+            mma_mxf8f6f4_ss(d_addr, adesc + 2, bdesc + 2, idesc_mxf8f6f4_m128(kTileN, 1), 1u, sfa_t, sfb_t);
+            mma_mxf8f6f4_ss(d_addr, adesc + 4, bdesc + 4, idesc_mxf8f6f4_m128(kTileN, 2), 1u, sfa_t, sfb_t);
+            mma_mxf8f6f4_ss(d_addr, adesc + 6, bdesc + 6, idesc_mxf8f6f4_m128(kTileN, 3), 1u, sfa_t, sfb_t);
+          } else {
+            for (int kb = 0; kb < tail_steps; ++kb)
+              mma_mxf8f6f4_ss(d_addr, adesc + 2 * kb, bdesc + 2 * kb, idesc_mxf8f6f4_m128(kTileN, kb), (kc | kb) != 0,
+                              sfa_t, sfb_t);
           }
           mma_commit(empty_bar(s));
         }
@@ -188,6 +202,7 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
           mma_commit(dfull_bar(d));
           mma_commit(sfa_empty_bar(q));
         }
+       }
       }
     }
   } else {
@@ -204,13 +219,14 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     bool ok = true;
     WorkItem w_next = {};
     if (static_cast<int>(blockIdx.x) < n_work) w_next = p.work[blockIdx.x];
-    for (int wi = blockIdx.x; ok && wi < n_work; wi += gridDim.x, ++item) {
-      const WorkItem w = w_next;
-      if (wi + static_cast<int>(gridDim.x) < n_work) w_next = p.work[wi + gridDim.x];  // in flight during the wait below
+    for (int wi = blockIdx.x; ok && wi < n_work; wi += gridDim.x) {
+     const WorkItem w = w_next;
+     if (wi + static_cast<int>(gridDim.x) < n_work) w_next = p.work[wi + gridDim.x];  // in flight during the wait below
+     for (int blk = 0; ok && blk < w.nblk; ++blk, ++item) {
       const uint32_t d = item & 1u;
       if (!mbar_wait(dfull_bar(d), (item >> 1) & 1u, abort_flag, p.status, ST_WAIT_DFULL)) { ok = false; break; }
       tc_fence_after();
-      const int n0 = w.ntile * kTileN;
+      const int n0 = (w.ntile + blk) * kTileN;
       const bool tok_ok = tok < w.ntok;
       const __nv_bfloat16 *bias_row = p.bias + static_cast<size_t>(w.expert) * p.R;
       const uint32_t acc = tmem_base + lane_field + d * kAccBufCols;
@@ -303,6 +319,7 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(dempty_bar(d));
+     }
     }
   }
 

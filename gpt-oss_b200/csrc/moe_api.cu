@@ -54,22 +54,20 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// Packed e2m1 weight codes [E][R][pitch bytes], declared to TMA as 4-bit elements that it expands to
-// the 8-bit containers of the block-scaled MMA (16U4_ALIGN16B).  That type wants the inner extent to be
-// a multiple of 128 elements, so it is rounded up: the last box of a row then reads a few bytes of the
-// next row (or of the slack behind the buffer), which meet zero-filled activations and scale 1.
-int make_weight_map(moe_ctx *c, CUtensorMap *m, const uint8_t *base, int E, int R, int K, int pitch) {
+// Weight tiles (LayerWeights::w1_tiles): every 16 KB tile starts with 240 rows x 64 bytes of packed e2m1 codes,
+// declared to TMA as 4-bit elements that it expands to the 8-bit containers of the block-scaled MMA
+// (16U4_ALIGN16B): dims {128 codes, 240 rows, tiles}, one box = the codes of one tile, a contiguous 15 KB read.
+int make_weight_map(moe_ctx *c, CUtensorMap *m, const uint8_t *base, size_t n_tiles) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(c, MOE_ERR_CUDA, "cuTensorMapEncodeTiled not available");
-  const cuuint64_t kvirt = static_cast<cuuint64_t>((K + 127) / 128) * 128;
-  const cuuint64_t dims[3] = {kvirt, static_cast<cuuint64_t>(R), static_cast<cuuint64_t>(E)};
-  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(pitch), static_cast<cuuint64_t>(R) * pitch};
+  const cuuint64_t dims[3] = {kChunkK, kTileN, static_cast<cuuint64_t>(n_tiles)};
+  const cuuint64_t strides[2] = {kChunkK / 2, kWTileStride};
   const cuuint32_t box[3] = {kChunkK, kTileN, 1};
   const cuuint32_t es[3] = {1, 1, 1};
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 3, const_cast<uint8_t *>(base), dims, strides, box, es,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(c, MOE_ERR_CUDA, "cuTensorMapEncodeTiled(weights E=%d R=%d K=%d) -> %d", E, R, K, (int)r);
+  if (r != CUDA_SUCCESS) return fail(c, MOE_ERR_CUDA, "cuTensorMapEncodeTiled(weights, %zu tiles) -> %d", n_tiles, (int)r);
   return MOE_OK;
 }
 
@@ -107,28 +105,38 @@ int dev_alloc(moe_ctx *c, T **p, size_t n) {
   return MOE_OK;
 }
 
-// E8M0 scales of one weight matrix -> [E][n_ntiles][n_kchunks][2 atoms][512]: the scales of a
-// work item's 240 weight rows for one 128-wide slice of k, in the order tcgen05.cp puts them into
-// tensor memory (row r of a 128-row atom, k block kb -> byte (r%32)*16 + (r/32)*4 + kb); 127
-// (scale 1) where no row or no block exists.
-void tile_scales(const uint8_t *raw /*[E][R][nblk]*/, int E, int R, int nblk, int n_ntiles, int n_kc,
-                 std::vector<uint8_t> &out) {
-  out.assign(static_cast<size_t>(E) * n_ntiles * n_kc * kSfbChunkBytes, 127);
+// One weight matrix -> the 16 KB tiles the GEMM streams (LayerWeights::w1_tiles).  codes: [E][R] rows of
+// row_bytes packed bytes at `pitch`; raw: E8M0 scales [E][R][nblk].  In a tile the scale of row r (of the tile's
+// 240), k block kb sits at byte (r%32)*16 + (r/32 %4)*4 + kb of atom r/128, the order tcgen05.cp puts them into
+// tensor memory; 127 (scale 1) and zero codes where no row or no block exists.
+void tile_weights(const uint8_t *codes, size_t pitch, size_t row_bytes, const uint8_t *raw, int E, int R, int nblk,
+                  int n_ntiles, int n_kc, std::vector<uint8_t> &out) {
+  out.assign(static_cast<size_t>(E) * n_ntiles * n_kc * kWTileStride, 0);
+  for (size_t t = 0; t < static_cast<size_t>(E) * n_ntiles * n_kc; ++t)
+    memset(&out[t * kWTileStride + kWTileCodes], 127, kSfbChunkBytes);
   for (int e = 0; e < E; ++e)
     for (int r = 0; r < R; ++r) {
-      const uint8_t *src = raw + (static_cast<size_t>(e) * R + r) * nblk;
+      const uint8_t *src_c = codes + (static_cast<size_t>(e) * R + r) * pitch;
+      const uint8_t *src_s = raw + (static_cast<size_t>(e) * R + r) * nblk;
       const int nt = r / kTileN, rr = r % kTileN, atom = rr / 128, ra = rr % 128;
+      uint8_t *tile0 = &out[(static_cast<size_t>(e) * n_ntiles + nt) * n_kc * kWTileStride];
+      for (int kc = 0; kc < n_kc; ++kc) {
+        const size_t off = static_cast<size_t>(kc) * (kChunkK / 2);
+        if (off < row_bytes)
+          memcpy(tile0 + static_cast<size_t>(kc) * kWTileStride + rr * (kChunkK / 2), src_c + off,
+                 std::min<size_t>(kChunkK / 2, row_bytes - off));
+      }
       for (int b = 0; b < nblk; ++b) {
         const int kc = b / 4, kb = b % 4;
-        out[((static_cast<size_t>(e) * n_ntiles + nt) * n_kc + kc) * kSfbChunkBytes + atom * kSfAtomBytes +
-            (ra % 32) * 16 + (ra / 32) * 4 + kb] = src[b];
+        tile0[static_cast<size_t>(kc) * kWTileStride + kWTileCodes + atom * kSfAtomBytes + (ra % 32) * 16 + (ra / 32) * 4 + kb] =
+            src_s[b];
       }
     }
 }
 
 void free_layer(LayerWeights &w) {
-  cudaFree(w.w1_codes); cudaFree(w.w1_scales); cudaFree(w.b1);
-  cudaFree(w.w2_codes); cudaFree(w.w2_scales); cudaFree(w.b2);
+  cudaFree(w.w1_tiles); cudaFree(w.b1);
+  cudaFree(w.w2_tiles); cudaFree(w.b2);
   cudaFree(w.w1_scales_raw); cudaFree(w.w2_scales_raw);
   cudaFree(w.router_w3); cudaFree(w.router_b);
   w = LayerWeights();
@@ -139,7 +147,7 @@ void free_layer(LayerWeights &w) {
 namespace moe {
 
 int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_bfloat16 *out_dev, unsigned flags,
-                 cudaStream_t s, const __nv_bfloat16 *t_local, int tp_rows_local) {
+                 cudaStream_t s, const __nv_bfloat16 *t_local, int tp_rows_local, const __nv_bfloat16 *residual) {
   if (layer < 0 || layer >= c->L || !t || rows <= 0 || rows > c->max_rows)
     return fail(c, MOE_ERR_INVALID, "moe_forward: layer %d rows %d (max %d)", layer, rows, c->max_rows);
   if (!out_dev && !(flags & MOE_FWD_PARTIAL_F32)) return fail(c, MOE_ERR_INVALID, "moe_forward: null output");
@@ -193,16 +201,16 @@ int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_b
   mark();
   const int add_b2 = c->cfg.tp_rank == 0 ? 1 : 0;
   if (flags & MOE_FWD_SIMT_GEMM) {
-    launch_simt_mlp1(w.w1_codes, c->pitch1, w.w1_scales_raw, w.b1, c->xperm, c->offsets, E, H, c->R1,
+    launch_simt_mlp1(w.w1_tiles, w.w1_scales_raw, w.b1, c->xperm, c->offsets, E, H, c->R1,
                      c->hbuf + c->joff, c->Kw, c->cfg.swiglu_limit, c->cfg.swiglu_alpha, P, s);
     mark();
-    launch_simt_mlp2(w.w2_codes, c->pitch2, w.w2_scales_raw, w.b2, add_b2, c->hbuf, c->offsets, E, c->Kw, H,
+    launch_simt_mlp2(w.w2_tiles, w.w2_scales_raw, w.b2, add_b2, c->hbuf, c->offsets, E, c->Kw, H,
                      c->ybuf, P, s);
   } else {
     GemmArgs a{};
     a.work = c->work1; a.n_work = c->n_work; a.K = H; a.R = c->R1;
     a.n_kchunks = (H + kChunkK - 1) / kChunkK; a.n_ntiles = n_nt1;
-    a.sfb = w.w1_scales; a.sfa = c->sfa_x; a.sfa_tile_stride = kSfAtomBytes; a.bias = w.b1; a.add_bias = 1;
+    a.w_tiles = w.w1_tiles; a.sfa = c->sfa_x; a.sfa_tile_stride = kSfAtomBytes; a.bias = w.b1; a.add_bias = 1;
     a.hq_out = c->hq + c->joff; a.y_out = nullptr; a.ld_out = c->Kw; a.h_exp = c->h_exp;
     a.limit = c->cfg.swiglu_limit; a.alpha = c->cfg.swiglu_alpha; a.status = c->status;
     launch_expert_gemm_mlp1(w.tm_w1, c->tm_x1, a, c->sm_count, s);
@@ -210,7 +218,7 @@ int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_b
     GemmArgs b = a;
     b.work = c->work2; b.n_work = c->n_work + 1; b.K = c->Kw; b.R = H;
     b.n_kchunks = (c->Kw + kChunkK - 1) / kChunkK; b.n_ntiles = n_nt2;
-    b.sfb = w.w2_scales; b.sfa = c->sfa_h; b.sfa_tile_stride = 0; b.bias = w.b2; b.add_bias = add_b2;
+    b.w_tiles = w.w2_tiles; b.sfa = c->sfa_h; b.sfa_tile_stride = 0; b.bias = w.b2; b.add_bias = add_b2;
     b.hq_out = nullptr; b.y_out = c->ybuf; b.ld_out = H;
     launch_expert_gemm_mlp2(w.tm_w2, c->tm_x2, b, c->sm_count, s);
   }
@@ -219,7 +227,7 @@ int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_b
     const bool partial = (flags & MOE_FWD_PARTIAL_F32) != 0;
     const bool keep_f32 = partial || (c->cfg.flags & MOE_CFG_KEEP_F32_OUT);
     launch_combine(c->ybuf, c->topk_idx, c->topk_w, c->pair_row, T, H, K, partial ? nullptr : out_dev,
-                   keep_f32 ? c->out_f32 : nullptr, s);
+                   keep_f32 ? c->out_f32 : nullptr, s, 0, nullptr, 0, 0, residual);
     mark();
   } else {
     // send half of the reduce-scatter inside the combine; then wait for every peer's rows and add the slots
@@ -227,7 +235,7 @@ int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_b
                    (c->cfg.flags & MOE_CFG_KEEP_F32_OUT) ? c->out_f32 : nullptr, s, tp, &c->peers, tp_rows_local, rank);
     ++c->tp_epoch_rs;
     launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, 1, c->tp_epoch_rs, c->status, s);
-    launch_tp_sum_slots(c->tp_partial, tp, tp_rows_local, H, out_dev, c->sm_count, s);
+    launch_tp_sum_slots(c->tp_partial, tp, tp_rows_local, H, out_dev, c->sm_count, s, residual);
     mark();
     c->launches += 2;
   }
@@ -313,6 +321,7 @@ int moe_create(const moe_config *cfg, moe_handle *out) {
   const size_t T = c->max_rows, P = c->max_pairs;
   int rc;
   if ((rc = dev_alloc(c, &c->t_in, T * c->H))) return rc;
+  if ((rc = dev_alloc(c, &c->t_norm, T * c->H))) return rc;
   if ((rc = dev_alloc(c, &c->logits, T * c->E))) return rc;
   // splits * rows never exceeds (sm_count / tiles) * 64 * tiles = 64 * sm_count
   if ((rc = dev_alloc(c, &c->router_part, std::max<size_t>(T, 64 * static_cast<size_t>(c->sm_count) + 64) * c->E))) return rc;
@@ -393,7 +402,7 @@ int moe_destroy(moe_handle c) {
   for (auto &w : c->layers) free_layer(w);
   for (cudaEvent_t e : c->prof_events) cudaEventDestroy(e);
   for (cudaEvent_t e : c->prof_pool) cudaEventDestroy(e);
-  cudaFree(c->t_in); cudaFree(c->logits); cudaFree(c->router_part); cudaFree(c->topk_idx); cudaFree(c->topk_w); cudaFree(c->counts);
+  cudaFree(c->t_in); cudaFree(c->t_norm); cudaFree(c->logits); cudaFree(c->router_part); cudaFree(c->topk_idx); cudaFree(c->topk_w); cudaFree(c->counts);
   cudaFree(c->offsets); cudaFree(c->pair_row); cudaFree(c->row_token); cudaFree(c->xperm); cudaFree(c->hbuf);
   cudaFree(c->ybuf); cudaFree(c->out_f32); cudaFree(c->out_bf16); cudaFree(c->work1); cudaFree(c->work2);
   cudaFree(c->n_work); cudaFree(c->status);
@@ -416,9 +425,7 @@ int moe_load_layer(moe_handle c, int layer, const uint8_t *w1_codes, const uint8
   // ---- this rank's shard, still in the reference layout -------------------
   // MLP1: rows [2*d0, 2*(d0+Dl)) of every expert (gate/up pairs stay adjacent);
   // MLP2: columns [k0, k0+Kw), the whole scale blocks that enclose the shard [d0, d0+Dl).
-  // Row pitch of the packed codes: K/2 bytes rounded up to 32 (a TMA requirement of the 4-bit
-  // element type); pad bytes are zero codes.
-  const size_t w1_row = H / 2, s1_row = H / 32, p1 = (w1_row + 31) / 32 * 32;
+  const size_t w1_row = H / 2, s1_row = H / 32, p1 = w1_row;
   std::vector<uint8_t> c1(static_cast<size_t>(E) * R1 * p1, 0), s1(static_cast<size_t>(E) * R1 * s1_row);
   std::vector<uint16_t> bb1(static_cast<size_t>(E) * R1);
   for (int e = 0; e < E; ++e) {
@@ -428,14 +435,12 @@ int moe_load_layer(moe_handle c, int layer, const uint8_t *w1_codes, const uint8
     memcpy(&s1[static_cast<size_t>(e) * R1 * s1_row], w1_scales + src_row0 * s1_row, static_cast<size_t>(R1) * s1_row);
     memcpy(&bb1[static_cast<size_t>(e) * R1], b1 + src_row0, static_cast<size_t>(R1) * 2);
   }
-  const size_t w2_row = Kw / 2, s2_row = Kw / 32, p2 = (w2_row + 31) / 32 * 32;
+  const size_t w2_row = Kw / 2, s2_row = Kw / 32, p2 = w2_row;
   std::vector<uint8_t> c2(static_cast<size_t>(E) * H * p2, 0), s2(static_cast<size_t>(E) * H * s2_row);
   for (size_t r = 0; r < static_cast<size_t>(E) * H; ++r) {
     memcpy(&c2[r * p2], w2_codes + r * (D / 2) + k0 / 2, w2_row);
     memcpy(&s2[r * s2_row], w2_scales + r * (D / 32) + k0 / 32, s2_row);
   }
-  c->pitch1 = static_cast<int>(p1);
-  c->pitch2 = static_cast<int>(p2);
   // 0xFF is the NaN encoding of E8M0; every other byte is a valid power of two for the tensor core
   for (const std::vector<uint8_t> *sv : {&s1, &s2})
     for (uint8_t b : *sv)
@@ -444,8 +449,10 @@ int moe_load_layer(moe_handle c, int layer, const uint8_t *w1_codes, const uint8
   const int n_nt1 = (R1 + kTileN - 1) / kTileN, n_kc1 = (H + kChunkK - 1) / kChunkK;
   const int n_nt2 = (H + kTileN - 1) / kTileN, n_kc2 = (Kw + kChunkK - 1) / kChunkK;
   std::vector<uint8_t> t1, t2;
-  tile_scales(s1.data(), E, R1, H / 32, n_nt1, n_kc1, t1);
-  tile_scales(s2.data(), E, H, Kw / 32, n_nt2, n_kc2, t2);
+  tile_weights(c1.data(), p1, w1_row, s1.data(), E, R1, H / 32, n_nt1, n_kc1, t1);
+  tile_weights(c2.data(), p2, w2_row, s2.data(), E, H, Kw / 32, n_nt2, n_kc2, t2);
+  std::vector<uint8_t>().swap(c1);
+  std::vector<uint8_t>().swap(c2);
 
   // router weight as three bf16 planes whose sum is the fp32 value exactly
   std::vector<uint16_t> w3(static_cast<size_t>(3) * E * H);
@@ -462,28 +469,24 @@ int moe_load_layer(moe_handle c, int layer, const uint8_t *w1_codes, const uint8
   }
 
   int rc;
-  if ((rc = dev_alloc(c, &w.w1_codes, c1.size()))) return rc;
-  if ((rc = dev_alloc(c, &w.w1_scales, t1.size()))) return rc;
+  if ((rc = dev_alloc(c, &w.w1_tiles, t1.size()))) return rc;
   if ((rc = dev_alloc(c, &w.w1_scales_raw, s1.size()))) return rc;
   if ((rc = dev_alloc(c, &w.b1, bb1.size()))) return rc;
-  if ((rc = dev_alloc(c, &w.w2_codes, c2.size()))) return rc;
-  if ((rc = dev_alloc(c, &w.w2_scales, t2.size()))) return rc;
+  if ((rc = dev_alloc(c, &w.w2_tiles, t2.size()))) return rc;
   if ((rc = dev_alloc(c, &w.w2_scales_raw, s2.size()))) return rc;
   if ((rc = dev_alloc(c, &w.b2, static_cast<size_t>(E) * H))) return rc;
   if ((rc = dev_alloc(c, &w.router_w3, w3.size()))) return rc;
   if ((rc = dev_alloc(c, &w.router_b, static_cast<size_t>(E)))) return rc;
-  CU_TRY(c, cudaMemcpy(w.w1_codes, c1.data(), c1.size(), cudaMemcpyHostToDevice));
-  CU_TRY(c, cudaMemcpy(w.w1_scales, t1.data(), t1.size(), cudaMemcpyHostToDevice));
+  CU_TRY(c, cudaMemcpy(w.w1_tiles, t1.data(), t1.size(), cudaMemcpyHostToDevice));
   CU_TRY(c, cudaMemcpy(w.w1_scales_raw, s1.data(), s1.size(), cudaMemcpyHostToDevice));
   CU_TRY(c, cudaMemcpy(w.b1, bb1.data(), bb1.size() * 2, cudaMemcpyHostToDevice));
-  CU_TRY(c, cudaMemcpy(w.w2_codes, c2.data(), c2.size(), cudaMemcpyHostToDevice));
-  CU_TRY(c, cudaMemcpy(w.w2_scales, t2.data(), t2.size(), cudaMemcpyHostToDevice));
+  CU_TRY(c, cudaMemcpy(w.w2_tiles, t2.data(), t2.size(), cudaMemcpyHostToDevice));
   CU_TRY(c, cudaMemcpy(w.w2_scales_raw, s2.data(), s2.size(), cudaMemcpyHostToDevice));
   CU_TRY(c, cudaMemcpy(w.b2, b2, static_cast<size_t>(E) * H * 2, cudaMemcpyHostToDevice));
   CU_TRY(c, cudaMemcpy(w.router_w3, w3.data(), w3.size() * 2, cudaMemcpyHostToDevice));
   CU_TRY(c, cudaMemcpy(w.router_b, router_b, static_cast<size_t>(E) * 4, cudaMemcpyHostToDevice));
-  if ((rc = make_weight_map(c, &w.tm_w1, w.w1_codes, E, R1, H, c->pitch1))) return rc;
-  if ((rc = make_weight_map(c, &w.tm_w2, w.w2_codes, E, H, Kw, c->pitch2))) return rc;
+  if ((rc = make_weight_map(c, &w.tm_w1, w.w1_tiles, static_cast<size_t>(E) * n_nt1 * n_kc1))) return rc;
+  if ((rc = make_weight_map(c, &w.tm_w2, w.w2_tiles, static_cast<size_t>(E) * n_nt2 * n_kc2))) return rc;
   w.loaded = true;
   return MOE_OK;
 }
@@ -588,6 +591,7 @@ int moe_get_debug(moe_handle c, int which, void *dst, size_t bytes) {
     case MOE_DBG_OUT_F32: src = c->out_f32; have = T * c->H * 4; break;
     case MOE_DBG_STATUS: src = c->status; have = 4096 * 4; break;
     case MOE_DBG_GATHER: src = c->t_in; have = static_cast<size_t>(c->max_rows) * c->H * 2; break;
+    case MOE_DBG_TNORM: src = c->t_norm; have = static_cast<size_t>(c->max_rows) * c->H * 2; break;
     case MOE_DBG_YBUF: src = c->ybuf; have = T * c->K * c->H * 4; break;
     default: return fail(c, MOE_ERR_INVALID, "moe_get_debug: unknown item %d", which);
   }

@@ -21,7 +21,10 @@ constexpr int kChunkK = 128;       // reduction elements per shared-memory stage
 constexpr int kTokTile = 64;       // token rows per work item
 constexpr int kTileM = 2 * kTokTile;  // UMMA M: each token contributes a high and a low e4m3 row
 constexpr int kSfAtomBytes = 512;  // scale factors of 128 rows x 4 k-blocks, tensor-memory order
-constexpr int kSfbChunkBytes = 2 * kSfAtomBytes;  // weight scales of one stage (256 rows)
+constexpr int kSfbChunkBytes = 2 * kSfAtomBytes;  // weight scales of one tile (240 rows in two atoms)
+constexpr int kWTileCodes = kTileN * kChunkK / 2;  // 15360 bytes of packed codes per weight tile
+constexpr int kWTileStride = kWTileCodes + kSfbChunkBytes;  // 16384: codes, then scales
+static_assert(kWTileStride == 16384, "weight tiles are 16 KB");
 
 // Device status bits (MOE_DBG_STATUS).
 enum : unsigned {
@@ -47,14 +50,16 @@ struct TpPeers {
 };
 constexpr int kTpBufs = 5;
 
-// One work item of the grouped GEMM.
+// One work item of the grouped GEMM: one token tile against one or two adjacent kTileN-row blocks of the
+// expert's weight matrix (two, except for the last block of an odd count).
 struct __align__(16) WorkItem {
   int expert;  // expert index
-  int ntile;   // kTileN-row block of that expert's weight matrix
+  int ntile;   // first kTileN-row block of that expert's weight matrix
   int tile;    // global token-tile index (rows tile*kTileM .. of the quantised activations)
   int row0;    // first permuted row of the token tile
   int ntok;    // valid token rows in the tile (1..kTokTile)
-  int pad[3];
+  int nblk;    // row blocks in this item: 1 or 2
+  int pad[2];
 };
 
 struct GemmArgs {
@@ -64,7 +69,7 @@ struct GemmArgs {
   int R;          // weight rows per expert on this rank
   int n_kchunks;  // ceil(K / kChunkK)
   int n_ntiles;   // ceil(R / kTileN)
-  const uint8_t *sfb;         // weight scales [E][n_ntiles][n_kchunks][2 atoms][512], 127 where no block exists
+  const uint8_t *w_tiles;     // weight tiles [E][n_ntiles][n_kchunks][kWTileStride], see LayerWeights::w1_tiles
   const uint8_t *sfa;         // activation scales, one 512-byte atom per token tile
   int sfa_tile_stride;        // bytes between token tiles' atoms (0: one atom shared by all tiles)
   const __nv_bfloat16 *bias;  // [E][R]
@@ -79,11 +84,12 @@ struct GemmArgs {
 
 struct LayerWeights {
   bool loaded = false;
-  uint8_t *w1_codes = nullptr;   // [E, R1, pitch1] packed e2m1, pitch = K/2 rounded up to 32 bytes
-  uint8_t *w1_scales = nullptr;  // repacked, see GemmArgs::sfb
+  // MLP1 weights as the GEMM streams them: one 16 KB tile per (expert, 240-row block, 128-wide slice of k),
+  // tiles of a block in k order: [240 rows x 64 bytes of packed e2m1 codes][two 512-byte E8M0 scale atoms in
+  // the order tcgen05.cp wants].  Rows or k beyond the matrix hold zero codes and scale 1 (byte 127).
+  uint8_t *w1_tiles = nullptr;
   __nv_bfloat16 *b1 = nullptr;   // [E, R1]
-  uint8_t *w2_codes = nullptr;   // [E, H, Dl/2]
-  uint8_t *w2_scales = nullptr;
+  uint8_t *w2_tiles = nullptr;   // MLP2 weights [E, H, Kw], same tiling
   __nv_bfloat16 *b2 = nullptr;   // [E, H]
   // raw (row-major, unpadded) scales for the validation GEMM
   uint8_t *w1_scales_raw = nullptr;  // [E, R1, H/32]
@@ -109,6 +115,7 @@ struct moe_ctx {
 
   // run state (names of the reference's GPURunState fields in comments)
   __nv_bfloat16 *t_in = nullptr;    // gather_x_g          [max_rows, H]
+  __nv_bfloat16 *t_norm = nullptr;  // t                   [max_rows, H]  RMS-normalised rows of moe_block()
   float *logits = nullptr;          // router_score_g      [max_rows, E]
   float *router_part = nullptr;     // split-k partial sums of the router [splits, rows, E]
   int *topk_idx = nullptr;          // topk_i_g            [max_rows, K]
@@ -126,7 +133,6 @@ struct moe_ctx {
   int *tile_base = nullptr;         // first token tile of each expert [E+1]
   int max_tiles = 0;
   int h_exp = 0;                    // hq holds e4m3(h * 2^-h_exp)
-  int pitch1 = 0, pitch2 = 0;       // bytes per packed weight row (MLP1, MLP2)
   float *ybuf = nullptr;            // expert_output_partial [max_pairs, H] fp32
   float *out_f32 = nullptr;         // fp32 block output   [max_rows, H] (debug / TP partial)
   __nv_bfloat16 *out_bf16 = nullptr;// e_agg_g             [max_rows, H]
@@ -171,7 +177,10 @@ void launch_gather_rows(const __nv_bfloat16 *t, const int *row_token, const int 
                         int H, int max_pairs, cudaStream_t s);
 void launch_combine(const float *y, const int *topk_idx, const float *topk_w, const int *pair_row, int T, int H,
                     int K, __nv_bfloat16 *out_bf16, float *out_f32, cudaStream_t s, int tp = 0,
-                    const TpPeers *peers = nullptr, int rows_local = 0, int rank = 0);
+                    const TpPeers *peers = nullptr, int rows_local = 0, int rank = 0,
+                    const __nv_bfloat16 *residual = nullptr);
+void launch_rmsnorm_rows(const __nv_bfloat16 *x, const __nv_bfloat16 *w, __nv_bfloat16 *t, int rows, int H,
+                         cudaStream_t s);
 
 // expert_gemm_sm100.cu
 cudaError_t expert_gemm_init();
@@ -186,15 +195,15 @@ void launch_tp_allgather_push(const __nv_bfloat16 *src, int rows_local, int H, c
 void launch_tp_signal_wait(const TpPeers &peers, uint32_t *my_flags, int tp, int rank, int phase, uint32_t epoch,
                            unsigned int *status, cudaStream_t s);
 void launch_tp_sum_slots(const __nv_bfloat16 *landing, int tp, int rows_local, int H, __nv_bfloat16 *out, int sm_count,
-                         cudaStream_t s);
+                         cudaStream_t s, const __nv_bfloat16 *residual = nullptr);
 void launch_tp_reduce_scatter_pull(const TpPeers &peers, int tp, int rank, int rows_local, int H, __nv_bfloat16 *out,
                                    int sm_count, cudaStream_t s);
 
 // expert_gemm_simt.cu (validation path)
-void launch_simt_mlp1(const uint8_t *codes, int pitch, const uint8_t *scales_raw, const __nv_bfloat16 *bias,
+void launch_simt_mlp1(const uint8_t *w_tiles, const uint8_t *scales_raw, const __nv_bfloat16 *bias,
                       const __half *x, const int *offsets, int E, int H, int R1, __half *h_out, int ld_h,
                       float limit, float alpha, int n_rows, cudaStream_t s);
-void launch_simt_mlp2(const uint8_t *codes, int pitch, const uint8_t *scales_raw, const __nv_bfloat16 *bias,
+void launch_simt_mlp2(const uint8_t *w_tiles, const uint8_t *scales_raw, const __nv_bfloat16 *bias,
                       int add_bias, const __half *h, const int *offsets, int E, int Dl, int H, float *y_out,
                       int n_rows, cudaStream_t s);
 
@@ -202,6 +211,7 @@ void launch_simt_mlp2(const uint8_t *codes, int pitch, const uint8_t *scales_raw
 // gather buffer, t_local this rank's rows; routing is computed for the local rows only and exchanged, the
 // combine pushes each row's partial to the rank that owns it, and out_dev receives this rank's summed rows.
 int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int T, __nv_bfloat16 *out_dev, unsigned flags,
-                 cudaStream_t s, const __nv_bfloat16 *t_local, int tp_rows_local);
+                 cudaStream_t s, const __nv_bfloat16 *t_local, int tp_rows_local,
+                 const __nv_bfloat16 *residual = nullptr);
 
 }  // namespace moe

@@ -149,6 +149,23 @@ int moe_tp_forward(moe_handle c, int layer, const void *t_local, int rows_local,
                       static_cast<const __nv_bfloat16 *>(t_local), rows_local);
 }
 
+int moe_block(moe_handle c, int layer, void *x_dev, const void *rms_w_dev, int rows_local, unsigned flags, void *stream) {
+  if (!c || !x_dev || !rms_w_dev) return MOE_ERR_INVALID;
+  int rc = check_tp_call(c, rows_local, "moe_block");
+  if (rc != MOE_OK) return rc;
+  const int tp = c->cfg.tp_size;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  __nv_bfloat16 *x = static_cast<__nv_bfloat16 *>(x_dev);
+  // step 0: t = rmsnorm(x) * w; the last kernel of the block adds its result to x in place
+  launch_rmsnorm_rows(x, static_cast<const __nv_bfloat16 *>(rms_w_dev), c->t_norm, rows_local, c->H, s);
+  c->launches += 1;
+  flags &= ~MOE_FWD_PARTIAL_F32;
+  if (tp > 1)
+    return forward_impl(c, layer, static_cast<const __nv_bfloat16 *>(c->peers.gather[c->cfg.tp_rank]), rows_local * tp, x,
+                        flags, s, c->t_norm, rows_local, x);
+  return forward_impl(c, layer, c->t_norm, rows_local, x, flags, s, nullptr, 0, x);
+}
+
 int moe_tp_forward_host(moe_handle c, int layer, const void *t_local_host, int rows_local, void *out_local_host,
                         unsigned flags) {
   if (!c || !t_local_host || !out_local_host) return MOE_ERR_INVALID;

@@ -342,26 +342,28 @@ build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ cou
   }
   if (tid == 0 && s_running != cnt) atomicOr(status, ST_BAD_INDEX);
 
-  // work items: one per (token tile of kTokTile rows, block of kTileN weight rows); items that share a
+  // work items: one per (token tile of kTokTile rows, PAIR of kTileN-row weight blocks); items that share a
   // weight block are adjacent so that block is fetched from HBM once and re-read from L2
   for (int which = 0; which < 2; ++which) {
     const int nn = which ? n_ntiles2 : n_ntiles1;
+    const int np = (nn + 1) / 2;
     WorkItem *work = which ? work2 : work1;
     const int cap = which ? max_work2 : max_work1;
-    const int start = tiles_before * nn;
-    for (int i = tid; i < ntt * nn; i += blockDim.x) {
-      const int ntile = i / ntt, tt = i % ntt;
+    const int start = tiles_before * np;
+    for (int i = tid; i < ntt * np; i += blockDim.x) {
+      const int pr = i / ntt, tt = i % ntt;
       WorkItem it;
       it.expert = e;
-      it.ntile = ntile;
+      it.ntile = 2 * pr;
       it.tile = tiles_before + tt;
       it.row0 = off + tt * kTokTile;
       it.ntok = min(kTokTile, cnt - tt * kTokTile);
-      it.pad[0] = it.pad[1] = it.pad[2] = 0;
+      it.nblk = min(2, nn - 2 * pr);
+      it.pad[0] = it.pad[1] = 0;
       if (start + i < cap) work[start + i] = it;
       else atomicOr(status, ST_BAD_INDEX);
     }
-    if (e == E - 1 && tid == 0) n_work[which] = min((tiles_before + ntt) * nn, cap);
+    if (e == E - 1 && tid == 0) n_work[which] = min((tiles_before + ntt) * np, cap);
   }
 }
 
@@ -506,7 +508,8 @@ void launch_gather_rows(const __nv_bfloat16 *t, const int *row_token, const int 
 __global__ void __launch_bounds__(256)
 combine_kernel(const float *__restrict__ y, const int *__restrict__ topk_idx, const float *__restrict__ topk_w,
                const int *__restrict__ pair_row, int T, int H, int K, __nv_bfloat16 *__restrict__ out_bf16,
-               float *__restrict__ out_f32, int tp, TpPeers peers, int rows_local, int rank) {
+               float *__restrict__ out_f32, int tp, TpPeers peers, int rows_local, int rank,
+               const __nv_bfloat16 *__restrict__ residual) {
   const int t = blockIdx.x;
   // tensor-parallel call: the row's bf16 partial goes straight into slot `rank` of the landing buffer of the
   // rank that owns row t (a peer store over NVLink), which is the send half of the reduce-scatter
@@ -536,6 +539,13 @@ combine_kernel(const float *__restrict__ y, const int *__restrict__ topk_idx, co
       acc.w = __fadd_rn(acc.w, __fmul_rn(v.w, wt[k]));
     }
     if (out_f32 != nullptr) reinterpret_cast<float4 *>(out_f32 + static_cast<size_t>(t) * H)[i] = acc;
+    if (residual != nullptr) {  // x += block output (accumulate_kernel_bf16, kernels/other_kernels.hpp:18-37), one rounding
+      const uint2 r = __ldg(reinterpret_cast<const uint2 *>(residual + static_cast<size_t>(t) * H) + i);
+      acc.x += __uint_as_float(r.x << 16);
+      acc.y += __uint_as_float(r.x & 0xffff0000u);
+      acc.z += __uint_as_float(r.y << 16);
+      acc.w += __uint_as_float(r.y & 0xffff0000u);
+    }
     if (out_bf16 != nullptr) {
       const __nv_bfloat162 a = __floats2bfloat162_rn(acc.x, acc.y), b = __floats2bfloat162_rn(acc.z, acc.w);
       uint2 o;
@@ -548,10 +558,61 @@ combine_kernel(const float *__restrict__ y, const int *__restrict__ topk_idx, co
 
 void launch_combine(const float *y, const int *topk_idx, const float *topk_w, const int *pair_row, int T, int H,
                     int K, __nv_bfloat16 *out_bf16, float *out_f32, cudaStream_t s, int tp, const TpPeers *peers,
-                    int rows_local, int rank) {
+                    int rows_local, int rank, const __nv_bfloat16 *residual) {
   TpPeers pv = {};
   if (tp > 0 && peers != nullptr) pv = *peers;
-  combine_kernel<<<T, 256, 0, s>>>(y, topk_idx, topk_w, pair_row, T, H, K, out_bf16, out_f32, tp, pv, rows_local, rank);
+  combine_kernel<<<T, 256, 0, s>>>(y, topk_idx, topk_w, pair_row, T, H, K, out_bf16, out_f32, tp, pv, rows_local, rank,
+                                   residual);
+}
+
+// ---------------------------------------------------------------------------
+// Pre-MoE RMSNorm, step 0 of moe_gpu / moe_gpu_120b: t = w * (x / sqrt(mean(x^2) + 1e-5)), bf16 in
+// and out, sum of squares in double.  Reference: rmsnorm_kernel_bf16_io (kernels/rmsnorm.hpp:115-164)
+// and rmsnorm of the CPU path (run.cpp:320-333).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+rmsnorm_rows_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ w,
+                    __nv_bfloat16 *__restrict__ t, int H) {
+  __shared__ double s_part[8];
+  const uint4 *src = reinterpret_cast<const uint4 *>(x + static_cast<size_t>(blockIdx.x) * H);
+  double ss = 0.0;
+  for (int c = threadIdx.x; c < H / 8; c += blockDim.x) {
+    const uint4 v = __ldg(src + c);
+    const uint32_t in[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float a = __uint_as_float(in[j] << 16), b = __uint_as_float(in[j] & 0xffff0000u);
+      ss += static_cast<double>(a) * a + static_cast<double>(b) * b;
+    }
+  }
+#pragma unroll
+  for (int off = 16; off; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  double tot = 0.0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += s_part[i];
+  const float inv = static_cast<float>(1.0 / sqrt(tot / H + 1e-5));
+  const uint4 *wv = reinterpret_cast<const uint4 *>(w);
+  uint4 *dst = reinterpret_cast<uint4 *>(t + static_cast<size_t>(blockIdx.x) * H);
+  for (int c = threadIdx.x; c < H / 8; c += blockDim.x) {
+    const uint4 v = __ldg(src + c), g = __ldg(wv + c);
+    const uint32_t in[4] = {v.x, v.y, v.z, v.w}, gn[4] = {g.x, g.y, g.z, g.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float a = __uint_as_float(gn[j] << 16) * (inv * __uint_as_float(in[j] << 16));
+      const float b = __uint_as_float(gn[j] & 0xffff0000u) * (inv * __uint_as_float(in[j] & 0xffff0000u));
+      const __nv_bfloat162 q = __floats2bfloat162_rn(a, b);
+      o[j] = *reinterpret_cast<const uint32_t *>(&q);
+    }
+    dst[c] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+void launch_rmsnorm_rows(const __nv_bfloat16 *x, const __nv_bfloat16 *w, __nv_bfloat16 *t, int rows, int H,
+                         cudaStream_t s) {
+  rmsnorm_rows_kernel<<<rows, 256, 0, s>>>(x, w, t, H);
 }
 
 // ---------------------------------------------------------------------------

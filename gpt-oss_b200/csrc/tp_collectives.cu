@@ -91,12 +91,22 @@ tp_reduce_scatter_pull_kernel(TpPeers peers, int tp, size_t slot_vec, size_t n_v
 // out[i] = bf16( sum over slots s = 0..tp-1 of landing[s][i] ): the receive half of the reduce-scatter when
 // every rank has pushed its partial rows into this rank's landing buffer (fp32 adds in rank order).
 __global__ void __launch_bounds__(256)
-tp_sum_slots_kernel(const uint4 *__restrict__ landing, int tp, size_t n_vec, uint4 *__restrict__ out) {
+tp_sum_slots_kernel(const uint4 *__restrict__ landing, int tp, size_t n_vec, uint4 *__restrict__ out,
+                    const uint4 *__restrict__ residual) {
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
   for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    if (residual != nullptr) {  // x += block output, folded into the same pass
+      const uint4 v = residual[i];
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[2 * j] = __uint_as_float(w[j] << 16);
+        acc[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+      }
+    }
     for (int r = 0; r < tp; ++r) {
       const uint4 v = landing[static_cast<size_t>(r) * n_vec + i];
       const uint32_t w[4] = {v.x, v.y, v.z, v.w};
@@ -117,11 +127,12 @@ tp_sum_slots_kernel(const uint4 *__restrict__ landing, int tp, size_t n_vec, uin
 }
 
 void launch_tp_sum_slots(const __nv_bfloat16 *landing, int tp, int rows_local, int H, __nv_bfloat16 *out, int sm_count,
-                         cudaStream_t s) {
+                         cudaStream_t s, const __nv_bfloat16 *residual) {
   const size_t n_vec = static_cast<size_t>(rows_local) * H / 8;
   const int blocks = static_cast<int>(std::min<size_t>((n_vec + 255) / 256, static_cast<size_t>(sm_count) * 4));
   tp_sum_slots_kernel<<<std::max(blocks, 1), 256, 0, s>>>(reinterpret_cast<const uint4 *>(landing), tp, n_vec,
-                                                          reinterpret_cast<uint4 *>(out));
+                                                          reinterpret_cast<uint4 *>(out),
+                                                          reinterpret_cast<const uint4 *>(residual));
 }
 
 void launch_tp_allgather_push(const __nv_bfloat16 *src, int rows_local, int H, const TpPeers &peers, int tp, int rank,

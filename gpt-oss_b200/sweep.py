@@ -37,7 +37,7 @@ def sweep_tokens(args):
     import torch
     pkg = importlib.import_module("gpt-oss_b200")
     synth = pkg.synth
-    E, H, D, K = 128, 2880, 2880, 4
+    E, H, D, K = args.experts, 2880, 2880, 4
     hbm, tc = _peaks()
     layer = synth.make_layer(E, H, D, seed=0, zipf_s=args.zipf)
     rows = [int(x) for x in args.rows.split(",")]
@@ -133,6 +133,7 @@ def main():
     ap.add_argument("--zipf", type=float, default=None)
     ap.add_argument("--rows", default=None)
     ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--experts", type=int, default=128, help="tokens: experts of the layer (32 = the 20B shape)")
     args = ap.parse_args()
     sys.path.insert(0, ROOT)
     if args.what == "tokens":

@@ -85,6 +85,18 @@ def make_tokens(n_tokens: int, hidden: int, seed: int = 0) -> np.ndarray:
     return f32_to_bf16_bits(t)
 
 
+def make_residual(n_tokens: int, hidden: int, seed: int = 0) -> tuple[np.ndarray, np.ndarray]:
+    """Residual-stream rows x [T, H] (row scales spread over two decades, a few outlier channels, as a
+    residual stream has) and an RMSNorm gain [H] around 1, both as bf16 bit patterns."""
+    rng = np.random.Generator(np.random.Philox([seed, 0x726573]))
+    x = rng.normal(0.0, 1.0, size=(n_tokens, hidden)).astype(np.float32)
+    x *= np.exp(rng.uniform(np.log(0.2), np.log(20.0), size=(n_tokens, 1))).astype(np.float32)
+    hot = rng.choice(hidden, size=max(hidden // 64, 1), replace=False)
+    x[:, hot] *= 8.0
+    gain = rng.normal(1.0, 0.25, size=hidden).astype(np.float32)
+    return f32_to_bf16_bits(x), f32_to_bf16_bits(gain)
+
+
 def weight_bytes_per_expert(hidden: int, inter: int) -> int:
     """MXFP4 codes + E8M0 scales + bf16 biases of one expert (both MLPs)."""
     w1 = 2 * inter * hidden

@@ -92,6 +92,14 @@ int moe_shard_range(int intermediate_dim, int tp_size, int tp_rank, int *start, 
 int moe_forward(moe_handle h, int layer, const void *t_dev, int rows, void *out_dev, unsigned flags,
                 void *stream);
 
+/* Replaces moe_gpu()/moe_gpu_120b() as a whole (getp_run.cpp:2540, :2896), steps 0-10: the residual
+ * stream rows x_dev (bf16 [rows_local, H], this rank's rows) are RMS-normalised with the bf16 gain
+ * rms_w_dev [H] (rmsnorm_kernel_bf16_io, kernels/rmsnorm.hpp:115-164), go through the block (through
+ * the tensor-parallel exchange when tp_size > 1; every rank of the group calls), and receive the
+ * result in place: x += MoE(rmsnorm(x)) (accumulate_kernel_bf16, kernels/other_kernels.hpp:18-37). */
+int moe_block(moe_handle h, int layer, void *x_dev, const void *rms_w_dev, int rows_local, unsigned flags,
+              void *stream);
+
 /* Same call for HOST buffers (pinned memory from moe_host_alloc copies
  * asynchronously): host->device copy, the block, device->host copy, then waits
  * and returns the device status. */
@@ -169,7 +177,8 @@ enum {
   MOE_DBG_OUT_F32 = 7,  /* f32 [rows, H]    block output before the bf16 rounding (MOE_CFG_KEEP_F32_OUT) */
   MOE_DBG_STATUS = 8,   /* u32 [4096]       device status word (first element) and diagnostics */
   MOE_DBG_YBUF = 10,    /* f32 [rows*K, H]  MLP2 output, permuted rows (expert_output_partial_g) */
-  MOE_DBG_GATHER = 11   /* bf16 [rows, H]   all-gather destination of the TP group (gather_x_g) */
+  MOE_DBG_GATHER = 11,  /* bf16 [rows, H]   all-gather destination of the TP group (gather_x_g) */
+  MOE_DBG_TNORM = 12    /* bf16 [rows_local, H]  RMS-normalised rows of the last moe_block() (state.t) */
 };
 int moe_get_debug(moe_handle h, int which, void *host_dst, size_t bytes);
 

@@ -257,6 +257,45 @@ int oracle_moe_layer(const float *t, int T, int H, int D, int E, int K,
                                 topk_v, out);
 }
 
+/* Round-to-nearest-even float -> bf16 -> float (finite inputs). */
+static inline float round_bf16(float f) {
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  u += 0x7fffu + ((u >> 16) & 1u);
+  u &= 0xffff0000u;
+  memcpy(&f, &u, 4);
+  return f;
+}
+
+/*
+ * The block as forward() wraps it, run.cpp:657-747: t = rmsnorm(x) * gain,
+ * e_agg = MoE(t), x_out = x + e_agg (run.cpp:744-747).  With t_as_bf16 = 0 this
+ * is the CPU reference to the bit.  The reference's GPU path keeps x and t in
+ * bf16 (rmsnorm_kernel_bf16_io stores bf16, getp-csrc/kernels/rmsnorm.hpp:160;
+ * accumulate_kernel_bf16, getp-csrc/kernels/other_kernels.hpp:18-37):
+ * t_as_bf16 = 1 rounds t to bf16 before the router and the experts see it, and
+ * the caller compares x_out within bf16 rounding.
+ */
+int oracle_moe_block(const float *x, const float *gain, int T, int H, int D,
+                     int E, int K, float limit, const uint8_t *w1c,
+                     const uint8_t *w1s, const float *b1, const uint8_t *w2c,
+                     const uint8_t *w2s, const float *b2, const float *wr,
+                     const float *br, int t_as_bf16, float *t_out,
+                     float *logits, int *topk_i, float *topk_v, float *e_agg,
+                     float *x_out) {
+  oracle_rmsnorm(x, gain, T, H, t_out);
+  if (t_as_bf16)
+    for (size_t i = 0; i < (size_t)T * H; ++i)
+      t_out[i] = round_bf16(t_out[i]);
+  int rc = oracle_moe_layer(t_out, T, H, D, E, K, limit, w1c, w1s, b1, w2c, w2s,
+                            b2, wr, br, logits, topk_i, topk_v, e_agg);
+  if (rc)
+    return rc;
+  for (size_t i = 0; i < (size_t)T * H; ++i)
+    x_out[i] = x[i] + e_agg[i];
+  return 0;
+}
+
 int oracle_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -105,6 +105,33 @@ class Port:
         return logits, idx, w, out
 
 
+    def moe_block(self, layer: dict, x: np.ndarray, gain: np.ndarray, top_k: int = 4, limit: float = 7.0,
+                  t_as_bf16: bool = False):
+        """x [T,H] and gain [H] as float32 values.  Returns t, logits, idx, w, e_agg, x_out."""
+        p = _prep(layer)
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        gain = np.ascontiguousarray(gain, dtype=np.float32)
+        T, H = x.shape
+        E, D = layer["E"], layer["D"]
+        t = np.empty((T, H), dtype=np.float32)
+        logits = np.empty((T, E), dtype=np.float32)
+        idx = np.empty((T, top_k), dtype=np.int32)
+        w = np.empty((T, top_k), dtype=np.float32)
+        agg = np.empty((T, H), dtype=np.float32)
+        xo = np.empty((T, H), dtype=np.float32)
+        self.lib.oracle_moe_block.restype = C.c_int
+        rc = self.lib.oracle_moe_block(
+            _ptr(x, C.c_float), _ptr(gain, C.c_float), T, H, D, E, top_k, C.c_float(limit),
+            _ptr(p["w1_codes"], C.c_uint8), _ptr(p["w1_scales"], C.c_uint8), _ptr(p["b1"], C.c_float),
+            _ptr(p["w2_codes"], C.c_uint8), _ptr(p["w2_scales"], C.c_uint8), _ptr(p["b2"], C.c_float),
+            _ptr(p["router_w"], C.c_float), _ptr(p["router_b"], C.c_float), int(t_as_bf16),
+            _ptr(t, C.c_float), _ptr(logits, C.c_float), _ptr(idx, C.c_int), _ptr(w, C.c_float),
+            _ptr(agg, C.c_float), _ptr(xo, C.c_float))
+        if rc != 0:
+            raise RuntimeError(f"oracle_moe_block failed: {rc}")
+        return t, logits, idx, w, agg, xo
+
+
 def reference_available() -> bool:
     return os.path.exists(REF_SO)
 
@@ -157,6 +184,23 @@ class Reference:
             raise RuntimeError(f"reference RMSNorm did not reproduce the injected rows "
                                f"({bad} elements differ)")
         return logits, idx, w, out
+
+    def forward_block(self, x: np.ndarray, gain: np.ndarray):
+        """forward() with its own RMSNorm: x [T,H], gain [H] float32.  Returns t, logits, idx, w, e_agg."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        gain = np.ascontiguousarray(gain, dtype=np.float32)
+        T, H = x.shape
+        E = self.layer["E"]
+        t = np.empty((T, H), dtype=np.float32)
+        logits = np.empty((T, E), dtype=np.float32)
+        idx = np.empty((T, self.k), dtype=np.int32)
+        w = np.empty((T, self.k), dtype=np.float32)
+        agg = np.empty((T, H), dtype=np.float32)
+        self.lib.ref_moe_forward_block.restype = None
+        self.lib.ref_moe_forward_block(self.h, _ptr(x, C.c_float), _ptr(gain, C.c_float), T, _ptr(t, C.c_float),
+                                       _ptr(logits, C.c_float), _ptr(idx, C.c_int), _ptr(w, C.c_float),
+                                       _ptr(agg, C.c_float))
+        return t, logits, idx, w, agg
 
     def close(self):
         if self.h:

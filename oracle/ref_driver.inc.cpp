@@ -228,6 +228,34 @@ long ref_moe_forward(void *h, const float *t_rows, int T, float *logits,
   return mismatches;
 }
 
+/* The block with its real RMSNorm: row x and gain vector go in as they are
+ * (no identity trick), forward() normalises (run.cpp:657), runs the MoE and
+ * adds the residual.  state.t and state.e_agg are read back; state.x is not,
+ * because the final rmsnorm (run.cpp:750) overwrites it in place. */
+void ref_moe_forward_block(void *h, const float *x_rows, const float *gain, int T,
+                           float *t_out, float *logits, int *topk_i, float *topk_v,
+                           float *e_agg) {
+  RefMoe *m = reinterpret_cast<RefMoe *>(h);
+  RunState *s = &m->tr.state;
+  const int H = m->H;
+  memcpy(m->gain.data(), gain, (size_t)H * sizeof(float));
+  for (int i = 0; i < T; ++i) {
+    memcpy(m->row_in.data(), x_rows + (size_t)i * H, (size_t)H * sizeof(float));
+    /* experts are dequantised on demand: route the row first, as forward() will */
+    rmsnorm(s->t, m->row_in.data(), m->gain.data(), H);
+    matmul(s->router_score, s->t, m->tr.weights.w_router, H, m->E);
+    for (int e = 0; e < m->E; ++e) s->router_score[e] += m->tr.weights.b_router[e];
+    topk(s->topk_v, s->topk_i, s->router_score, m->E, m->K);
+    for (int k = 0; k < m->K; ++k) need_expert(m, s->topk_i[k]);
+    forward(&m->tr, /*token=*/0, /*pos=*/0);
+    memcpy(t_out + (size_t)i * H, s->t, (size_t)H * sizeof(float));
+    if (logits) memcpy(logits + (size_t)i * m->E, s->router_score, (size_t)m->E * sizeof(float));
+    if (topk_i) memcpy(topk_i + (size_t)i * m->K, s->topk_i, (size_t)m->K * sizeof(int));
+    if (topk_v) memcpy(topk_v + (size_t)i * m->K, s->topk_v, (size_t)m->K * sizeof(float));
+    memcpy(e_agg + (size_t)i * H, s->e_agg, (size_t)H * sizeof(float));
+  }
+}
+
 int ref_moe_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -39,4 +39,9 @@ GOLDEN_DIR = os.path.join(ROOT, "tests", "golden")
 
 
 def golden_cases():
-    return sorted(f[:-4] for f in os.listdir(GOLDEN_DIR) if f.endswith(".npz"))
+    return sorted(f[:-4] for f in os.listdir(GOLDEN_DIR) if f.endswith(".npz") and not f.startswith("block_"))
+
+
+def golden_block_cases():
+    """Fixtures of the block with its RMSNorm and residual add (reference forward(), run.cpp:657-747)."""
+    return sorted(f[:-4] for f in os.listdir(GOLDEN_DIR) if f.endswith(".npz") and f.startswith("block_"))

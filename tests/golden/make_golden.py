@@ -7,6 +7,8 @@ run.cpp's CPU part into oracle/_ref/libref_moe.so):
 
 Each fixture holds the outputs of the reference binary (router logits, top-k
 indices, softmax weights, block output e_agg) for one seeded synthetic layer.
+The block_* fixtures go through forward()'s own RMSNorm
+(residual rows x and a gain vector in, state.t and e_agg out).
 Small cases also store their inputs; the GPT-OSS-20B-shape case stores the
 seeds and a SHA-256 of the regenerated inputs instead (423 MB of weights).
 """
@@ -34,6 +36,12 @@ CASES = [
     ("shape20b_e32_h2880_d2880_t16", 32, 2880, 2880, 16, 0, 0, None, False),
 ]
 
+# The block with its own RMSNorm and the residual add (forward(), run.cpp:657-747): name, E, H, D, T, seeds
+BLOCK_CASES = [
+    ("block_e8_h64_d64_t12", 8, 64, 64, 12, 51, 52),
+    ("block_e16_h128_d96_t33", 16, 128, 96, 33, 61, 62),
+]
+
 LAYER_KEYS = ("w1_codes", "w1_scales", "b1", "w2_codes", "w2_scales", "b2", "router_w", "router_b")
 
 
@@ -48,7 +56,8 @@ def inputs_digest(layer, tokens) -> str:
 def main():
     oracle.build(quiet=False)
     here = os.path.dirname(os.path.abspath(__file__))
-    for name, E, H, D, T, ls, ts, zipf, store in CASES:
+    only_blocks = "--blocks" in sys.argv  # leave the older fixtures untouched
+    for name, E, H, D, T, ls, ts, zipf, store in ([] if only_blocks else CASES):
         layer = synth.make_layer(E, H, D, seed=ls, zipf_s=zipf)
         tokens = synth.make_tokens(T, H, seed=ts)
         ref = oracle.Reference(layer)
@@ -65,6 +74,17 @@ def main():
         path = os.path.join(here, name + ".npz")
         np.savez_compressed(path, **blob)
         print(f"{name}: {os.path.getsize(path)} bytes, out rms {np.sqrt((out ** 2).mean()):.4f}")
+    for name, E, H, D, T, ls, xs in BLOCK_CASES:
+        layer = synth.make_layer(E, H, D, seed=ls)
+        x_bits, gain_bits = synth.make_residual(T, H, seed=xs)
+        ref = oracle.Reference(layer)
+        t, logits, idx, w, agg = ref.forward_block(synth.bf16_bits_to_f32(x_bits), synth.bf16_bits_to_f32(gain_bits))
+        ref.close()
+        blob = dict(E=E, H=H, D=D, T=T, x=x_bits, gain=gain_bits, t=t, logits=logits, topk_i=idx, topk_v=w, e_agg=agg)
+        blob.update({k: layer[k] for k in LAYER_KEYS})
+        path = os.path.join(here, name + ".npz")
+        np.savez_compressed(path, **blob)
+        print(f"{name}: {os.path.getsize(path)} bytes, e_agg rms {np.sqrt((agg ** 2).mean()):.4f}")
 
 
 if __name__ == "__main__":

@@ -12,7 +12,7 @@ import numpy as np
 import pytest
 
 import oracle
-from conftest import GOLDEN_DIR, golden_cases
+from conftest import GOLDEN_DIR, golden_block_cases, golden_cases
 
 LAYER_KEYS = ("w1_codes", "w1_scales", "b1", "w2_codes", "w2_scales", "b2", "router_w", "router_b")
 
@@ -95,3 +95,36 @@ def test_topk_ties_prefer_lower_index(port):
     assert idx.tolist() == [[1, 2, 4, 3]]
     e = np.exp(np.array([0, 0, 0, -1.0]))
     np.testing.assert_allclose(w[0], e / e.sum(), rtol=1e-6)
+
+
+def load_block_case(name, synth):
+    z = np.load(os.path.join(GOLDEN_DIR, name + ".npz"))
+    layer = {k: z[k] for k in LAYER_KEYS}
+    layer.update(E=int(z["E"]), H=int(z["H"]), D=int(z["D"]))
+    return layer, z
+
+
+@pytest.mark.parametrize("name", golden_block_cases())
+def test_block_with_rmsnorm_matches_reference_golden(name, synth, port):
+    layer, z = load_block_case(name, synth)
+    x, gain = synth.bf16_bits_to_f32(z["x"]), synth.bf16_bits_to_f32(z["gain"])
+    t, logits, idx, w, agg, xo = port.moe_block(layer, x, gain)
+    assert np.array_equal(t, z["t"])          # rmsnorm, run.cpp:320-333
+    assert np.array_equal(logits, z["logits"])
+    assert np.array_equal(idx, z["topk_i"])
+    assert np.array_equal(w, z["topk_v"])
+    assert np.array_equal(agg, z["e_agg"])
+    assert np.array_equal(xo, x + z["e_agg"])  # residual, run.cpp:744-747
+
+
+@pytest.mark.skipif(not oracle.reference_available(), reason="oracle/_ref not built")
+def test_block_with_rmsnorm_matches_reference_live(synth, port):
+    layer = synth.make_layer(8, 96, 64, seed=71)
+    xb, gb = synth.make_residual(9, 96, seed=72)
+    x, gain = synth.bf16_bits_to_f32(xb), synth.bf16_bits_to_f32(gb)
+    ref = oracle.Reference(layer)
+    r = ref.forward_block(x, gain)
+    ref.close()
+    p = port.moe_block(layer, x, gain)
+    for a, b in zip(p[:5], r):
+        assert np.array_equal(a, b)

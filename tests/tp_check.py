@@ -53,6 +53,25 @@ def main():
     blk.synchronize()
     blk.rows = rows_local * world
     assert np.array_equal(blk.debug(pkg.DBG_GATHER), union), "all-gather buffer differs from the union of the ranks' rows"
+    # the reference's calling form over the group: x <- x + MoE(rmsnorm(x) * gain) on each rank's rows
+    x_bits, gain_bits = pkg.synth.make_residual(rows_local * world, H, seed=9)
+    xf, gf = pkg.synth.bf16_bits_to_f32(x_bits), pkg.synth.bf16_bits_to_f32(gain_bits)
+    _, b_logits, b_idx, _, b_agg, b_xo = oracle.Port().moe_block(layer, xf, gf, t_as_bf16=True)
+    sl = slice(rank * rows_local, (rank + 1) * rows_local)
+    d_x = torch.from_numpy(x_bits[sl].view(np.int16).copy()).cuda()
+    d_g = torch.from_numpy(gain_bits.view(np.int16).copy()).cuda()
+    blk.block(0, d_x.data_ptr(), d_g.data_ptr(), rows_local, 0, stream)
+    torch.cuda.synchronize()
+    blk.synchronize()
+    same = (np.sort(blk.debug(pkg.DBG_TOPK_IDX), axis=1) == np.sort(b_idx, axis=1)).all(axis=1)
+    srt = np.sort(b_logits, axis=1)[:, ::-1]
+    assert ((srt[:, 3] - srt[:, 4])[~same] < 1e-5).all(), "block form: routing differs with a clear logit gap"
+    got_x = pkg.synth.bf16_bits_to_f32(d_x.cpu().numpy().view(np.uint16)).astype(np.float64)
+    ok_rows = same[sl]
+    b_err = np.abs(got_x - b_xo[sl])[ok_rows]
+    b_rms = max(1.0, float(np.sqrt((b_agg.astype(np.float64) ** 2).mean())))
+    bound = (2e-2 * b_rms + 2.0 ** -8 * np.abs(b_xo[sl]))[ok_rows]
+    assert (b_err <= bound).all(), float((b_err - bound).max())
     dist.barrier()
     print(f"rank {rank}: tp_forward ok, mean rel {mean_rel:.2e}, max abs {err.max():.3e} (rms {rms:.2f})", flush=True)
     blk.close()
