@@ -33,7 +33,7 @@ EXPORTS = [
     "moe_create", "moe_destroy", "moe_load_layer", "moe_shard_range", "moe_forward", "moe_forward_host",
     "moe_synchronize", "moe_host_alloc", "moe_host_free", "moe_route_topk", "moe_get_debug",
     "moe_last_error", "moe_strerror", "moe_launch_count", "moe_profile_enable", "moe_profile_collect",
-    "moe_route_static", "moe_block", "moe_tp_export", "moe_tp_attach_ipc", "moe_tp_buffer", "moe_tp_attach_ptr",
+    "moe_route_static", "moe_block", "moe_forward_host_submit", "moe_forward_host_wait", "moe_tp_export", "moe_tp_attach_ipc", "moe_tp_buffer", "moe_tp_attach_ptr",
     "moe_tp_forward", "moe_tp_forward_host", "moe_tp_allgather", "moe_tp_reduce_scatter",
 ]
 TP_BUF_GATHER, TP_BUF_PARTIAL, TP_BUF_FLAGS, TP_BUF_TOPK_IDX, TP_BUF_TOPK_W = range(5)
@@ -94,6 +94,9 @@ def lib() -> C.CDLL:
         L.moe_tp_forward_host.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_uint]
         L.moe_tp_allgather.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
         L.moe_tp_reduce_scatter.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
+        L.moe_forward_host_submit.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_uint,
+                                              C.POINTER(C.c_longlong)]
+        L.moe_forward_host_wait.argtypes = [C.c_void_p, C.c_longlong]
         L.moe_block.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_uint, C.c_void_p]
         L.moe_profile_enable.argtypes = [C.c_void_p, C.c_int]
         L.moe_profile_collect.argtypes = [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_int)]
@@ -176,6 +179,19 @@ class MoeBlock:
                                             out.ctypes.data_as(C.c_void_p), flags))
         self.rows = rows
         return out
+
+    def forward_host_submit(self, layer: int, t_bits: np.ndarray, out: np.ndarray, flags: int = 0) -> int:
+        """Starts one batch (host arrays, ideally PinnedBuffer.array, kept alive until the wait) and returns
+        its ticket; up to three batches may be in flight."""
+        assert t_bits.dtype == np.uint16 and t_bits.flags.c_contiguous and out.flags.c_contiguous
+        ticket = C.c_longlong(-1)
+        self._check(self.L.moe_forward_host_submit(self.h, layer, t_bits.ctypes.data_as(C.c_void_p), t_bits.shape[0],
+                                                   out.ctypes.data_as(C.c_void_p), flags, C.byref(ticket)))
+        self.rows = t_bits.shape[0]
+        return ticket.value
+
+    def forward_host_wait(self, ticket: int):
+        self._check(self.L.moe_forward_host_wait(self.h, C.c_longlong(ticket)))
 
     def forward(self, layer: int, t_ptr: int, rows: int, out_ptr: int, flags: int = 0, stream: int = 0):
         """Device pointers; stream-ordered, does not wait."""

@@ -396,6 +396,14 @@ int moe_destroy(moe_handle c) {
   if (c->stream) { cudaStreamSynchronize(c->stream); cudaStreamDestroy(c->stream); }
   for (void *p : c->ipc_opened) cudaIpcCloseMemHandle(p);
   if (c->aux_stream) { cudaStreamSynchronize(c->aux_stream); cudaStreamDestroy(c->aux_stream); }
+  for (cudaStream_t st : {c->h2d_stream, c->d2h_stream})
+    if (st) { cudaStreamSynchronize(st); cudaStreamDestroy(st); }
+  for (HostSlot &hs : c->host_slots) {
+    cudaFree(hs.in); cudaFree(hs.out);
+    if (hs.status_host) cudaFreeHost(hs.status_host);
+    for (cudaEvent_t e : {hs.in_ready, hs.out_ready, hs.done})
+      if (e) cudaEventDestroy(e);
+  }
   if (c->ev_fork) cudaEventDestroy(c->ev_fork);
   if (c->ev_join) cudaEventDestroy(c->ev_join);
   cudaFree(c->tp_partial); cudaFree(c->tp_flags);
@@ -537,6 +545,79 @@ int moe_forward_host(moe_handle c, int layer, const void *t_host, int rows, void
     return fail(c, (st & ST_BAD_INDEX) ? MOE_ERR_STATE : MOE_ERR_TIMEOUT, "device status word 0x%x", st);
   }
   return MOE_OK;
+}
+
+namespace {
+
+// staging buffers, events and copy streams of the pipelined host entry points, made on first use
+int host_pipeline_init(moe_ctx *c) {
+  if (c->h2d_stream) return MOE_OK;
+  CU_TRY(c, cudaStreamCreateWithFlags(&c->h2d_stream, cudaStreamNonBlocking));
+  CU_TRY(c, cudaStreamCreateWithFlags(&c->d2h_stream, cudaStreamNonBlocking));
+  const size_t n = static_cast<size_t>(c->max_rows) * c->H;
+  for (HostSlot &hs : c->host_slots) {
+    int rc;
+    if ((rc = dev_alloc(c, &hs.in, n))) return rc;
+    if ((rc = dev_alloc(c, &hs.out, n))) return rc;
+    CU_TRY(c, cudaHostAlloc(reinterpret_cast<void **>(&hs.status_host), sizeof(unsigned), cudaHostAllocDefault));
+    CU_TRY(c, cudaEventCreateWithFlags(&hs.in_ready, cudaEventDisableTiming));
+    CU_TRY(c, cudaEventCreateWithFlags(&hs.out_ready, cudaEventDisableTiming));
+    CU_TRY(c, cudaEventCreateWithFlags(&hs.done, cudaEventDisableTiming));
+  }
+  return MOE_OK;
+}
+
+int host_slot_finish(moe_ctx *c, HostSlot &hs) {
+  CU_TRY(c, cudaEventSynchronize(hs.done));
+  hs.ticket = -1;
+  const unsigned st = *hs.status_host;
+  if (st) {
+    CU_TRY(c, cudaMemset(c->status, 0, sizeof(unsigned)));
+    return fail(c, (st & ST_BAD_INDEX) ? MOE_ERR_STATE : MOE_ERR_TIMEOUT, "device status word 0x%x", st);
+  }
+  return MOE_OK;
+}
+
+}  // namespace
+
+int moe_forward_host_submit(moe_handle c, int layer, const void *t_host, int rows, void *out_host, unsigned flags,
+                            long long *ticket) {
+  if (!c) return MOE_ERR_INVALID;
+  if (!t_host || !out_host || !ticket || rows <= 0 || rows > c->max_rows)
+    return fail(c, MOE_ERR_INVALID, "moe_forward_host_submit: bad arguments");
+  if (c->cfg.tp_size > 1) return fail(c, MOE_ERR_STATE, "moe_forward_host_submit: single-GPU handles only");
+  CU_TRY(c, cudaSetDevice(c->cfg.device));
+  int rc = host_pipeline_init(c);
+  if (rc != MOE_OK) return rc;
+  HostSlot &hs = c->host_slots[c->host_submitted % kHostSlots];
+  if (hs.ticket >= 0)
+    return fail(c, MOE_ERR_STATE, "moe_forward_host_submit: %d calls in flight, wait for ticket %lld first", kHostSlots,
+                hs.ticket);
+  const size_t bytes = static_cast<size_t>(rows) * c->H * 2;
+  // copy in | block | copy out, each on its own stream; the block of call n runs while call n+1 copies in and
+  // call n-1 copies out
+  CU_TRY(c, cudaMemcpyAsync(hs.in, t_host, bytes, cudaMemcpyHostToDevice, c->h2d_stream));
+  CU_TRY(c, cudaEventRecord(hs.in_ready, c->h2d_stream));
+  CU_TRY(c, cudaStreamWaitEvent(c->stream, hs.in_ready, 0));
+  rc = forward_impl(c, layer, hs.in, rows, hs.out, flags & ~MOE_FWD_PARTIAL_F32, c->stream, nullptr, 0);
+  if (rc != MOE_OK) return rc;
+  CU_TRY(c, cudaEventRecord(hs.out_ready, c->stream));
+  CU_TRY(c, cudaStreamWaitEvent(c->d2h_stream, hs.out_ready, 0));
+  CU_TRY(c, cudaMemcpyAsync(out_host, hs.out, bytes, cudaMemcpyDeviceToHost, c->d2h_stream));
+  CU_TRY(c, cudaMemcpyAsync(hs.status_host, c->status, sizeof(unsigned), cudaMemcpyDeviceToHost, c->d2h_stream));
+  CU_TRY(c, cudaEventRecord(hs.done, c->d2h_stream));
+  hs.ticket = c->host_submitted;
+  *ticket = c->host_submitted++;
+  return MOE_OK;
+}
+
+int moe_forward_host_wait(moe_handle c, long long ticket) {
+  if (!c) return MOE_ERR_INVALID;
+  if (ticket < 0 || ticket >= c->host_submitted) return fail(c, MOE_ERR_INVALID, "moe_forward_host_wait: unknown ticket %lld", ticket);
+  CU_TRY(c, cudaSetDevice(c->cfg.device));
+  HostSlot &hs = c->host_slots[ticket % kHostSlots];
+  if (hs.ticket != ticket) return MOE_OK;  // already waited for
+  return host_slot_finish(c, hs);
 }
 
 int moe_profile_enable(moe_handle c, int on) {

@@ -50,6 +50,16 @@ struct TpPeers {
 };
 constexpr int kTpBufs = 5;
 
+// One call in flight through moe_forward_host_submit: its own input and output staging, so that the copies of
+// neighbouring calls overlap the block of this one.
+constexpr int kHostSlots = 3;
+struct HostSlot {
+  __nv_bfloat16 *in = nullptr, *out = nullptr;   // [max_rows, H] each
+  unsigned int *status_host = nullptr;           // pinned copy of the device status word, taken after the block
+  cudaEvent_t in_ready = nullptr, out_ready = nullptr, done = nullptr;
+  long long ticket = -1;                         // call that owns the slot; -1: free
+};
+
 // One work item of the grouped GEMM: one token tile against one or two adjacent kTileN-row blocks of the
 // expert's weight matrix (two, except for the last block of an odd count).
 struct __align__(16) WorkItem {
@@ -147,6 +157,9 @@ struct moe_ctx {
   __nv_bfloat16 *tp_partial = nullptr;  // this rank's bf16 partial output [max_rows, H]
   uint32_t *tp_flags = nullptr;     // [2][kMaxTp], written by the peers
   uint64_t tp_attached = 0;         // bit (kTpBufs*r + which) set once rank r's buffer `which` is known
+  moe::HostSlot host_slots[moe::kHostSlots];
+  cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
+  long long host_submitted = 0;
   cudaStream_t aux_stream = nullptr;  // the all-gather push runs beside the router
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
   uint32_t tp_epoch = 0, tp_epoch_rs = 0;  // all-gather / reduce-scatter call counters

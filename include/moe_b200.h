@@ -105,6 +105,16 @@ int moe_block(moe_handle h, int layer, void *x_dev, const void *rms_w_dev, int r
  * and returns the device status. */
 int moe_forward_host(moe_handle h, int layer, const void *t_host, int rows, void *out_host, unsigned flags);
 
+/* The same call split in two so that the copies of one batch overlap the block of another: submit
+ * returns at once with a ticket; wait blocks until that batch's result is in out_host.  Up to three
+ * batches may be in flight (a fourth submit fails with MOE_ERR_STATE until the oldest was waited for);
+ * both host buffers must stay valid, and should be pinned (moe_host_alloc), until the wait returns.
+ * The reference has no counterpart: its forward_batch_gpu (getp_run.cpp:3254) copies tokens in, runs
+ * and copies logits out on one stream, blocking the host thread. */
+int moe_forward_host_submit(moe_handle h, int layer, const void *t_host, int rows, void *out_host,
+                            unsigned flags, long long *ticket);
+int moe_forward_host_wait(moe_handle h, long long ticket);
+
 /* Waits for the handle's stream work and reports MOE_ERR_TIMEOUT if any kernel
  * recorded a bounded wait that ran out. */
 int moe_synchronize(moe_handle h);

@@ -333,3 +333,43 @@ def test_block_form_20b_shape(pkg, synth, port):
     layer = synth.make_layer(32, 2880, 2880, seed=3)
     x_bits, gain_bits = synth.make_residual(48, 2880, seed=4)
     check_block_form(pkg, synth, port, layer, x_bits, gain_bits)
+
+
+def test_host_pipeline_submit_wait(pkg, synth):
+    """Batches in flight through submit/wait give the same bits as the blocking call, in any overlap;
+    a fourth submit without a wait is refused and the handle stays usable."""
+    E, H, D = 16, 256, 320
+    layer = synth.make_layer(E, H, D, seed=90)
+    batches = [synth.make_tokens(rows, H, seed=91 + i) for i, rows in enumerate((70, 128, 1, 99, 128, 33, 64))]
+    blk = pkg.MoeBlock(H, D, E, max_rows=128)
+    try:
+        blk.load_layer(0, layer)
+        want = [blk.forward_host(0, b).copy() for b in batches]
+        pin_in = [pkg.PinnedBuffer(b.shape, np.uint16) for b in batches]
+        pin_out = [pkg.PinnedBuffer(b.shape, np.uint16) for b in batches]
+        for p, b in zip(pin_in, batches):
+            p.array[:] = b
+        tickets = []
+        for i in range(len(batches)):
+            if len(tickets) == 3:
+                blk.forward_host_wait(tickets.pop(0))
+            tickets.append(blk.forward_host_submit(0, pin_in[i].array, pin_out[i].array))
+        for t in tickets:
+            blk.forward_host_wait(t)
+        for i, w in enumerate(want):
+            assert np.array_equal(pin_out[i].array, w), f"batch {i}"
+        # three in flight, a fourth is refused
+        ts = [blk.forward_host_submit(0, pin_in[i].array, pin_out[i].array) for i in range(3)]
+        with pytest.raises(pkg.MoeError) as ei:
+            blk.forward_host_submit(0, pin_in[3].array, pin_out[3].array)
+        assert ei.value.code == 6
+        for t in ts:
+            blk.forward_host_wait(t)
+        blk.forward_host_wait(ts[0])          # waiting twice is harmless
+        t = blk.forward_host_submit(0, pin_in[3].array, pin_out[3].array)
+        blk.forward_host_wait(t)
+        assert np.array_equal(pin_out[3].array, want[3])
+        for p in pin_in + pin_out:
+            p.free()
+    finally:
+        blk.close()
