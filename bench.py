@@ -43,7 +43,7 @@ SHAPE = dict(E=128, H=2880, D=2880, K=4)
 CPU_SAMPLE_TOKENS = 32
 # dram read+write bytes / algorithmic bytes of the MLP1 kernel, from the ncu capture summarised in
 # profiles/expert_gemm_mxf8f6f4_20bshape_t464.md (small case; traffic is proportional to the weights streamed)
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.015
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.034
 
 
 def tp_size_for(n_gpus: int, parallel: str, tp_arg: int) -> int:
