@@ -33,7 +33,8 @@ EXPORTS = [
     "moe_create", "moe_destroy", "moe_load_layer", "moe_shard_range", "moe_forward", "moe_forward_host",
     "moe_synchronize", "moe_host_alloc", "moe_host_free", "moe_route_topk", "moe_get_debug",
     "moe_last_error", "moe_strerror", "moe_launch_count", "moe_profile_enable", "moe_profile_collect",
-    "moe_route_static", "moe_block", "moe_forward_host_submit", "moe_forward_host_wait", "moe_tp_export", "moe_tp_attach_ipc", "moe_tp_buffer", "moe_tp_attach_ptr",
+    "moe_route_static", "moe_block", "moe_forward_host_submit", "moe_forward_host_wait",
+    "moe_quantize_mxfp4", "moe_load_layer_f32", "moe_tp_export", "moe_tp_attach_ipc", "moe_tp_buffer", "moe_tp_attach_ptr",
     "moe_tp_forward", "moe_tp_forward_host", "moe_tp_allgather", "moe_tp_reduce_scatter",
 ]
 TP_BUF_GATHER, TP_BUF_PARTIAL, TP_BUF_FLAGS, TP_BUF_TOPK_IDX, TP_BUF_TOPK_W = range(5)
@@ -97,6 +98,8 @@ def lib() -> C.CDLL:
         L.moe_forward_host_submit.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_uint,
                                               C.POINTER(C.c_longlong)]
         L.moe_forward_host_wait.argtypes = [C.c_void_p, C.c_longlong]
+        L.moe_quantize_mxfp4.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p]
+        L.moe_load_layer_f32.argtypes = [C.c_void_p, C.c_int] + [C.c_void_p] * 6
         L.moe_block.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_uint, C.c_void_p]
         L.moe_profile_enable.argtypes = [C.c_void_p, C.c_int]
         L.moe_profile_collect.argtypes = [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_int)]
@@ -110,6 +113,14 @@ def shard_range(inter: int, tp_size: int, tp_rank: int) -> tuple[int, int]:
     if rc != MOE_OK:
         raise MoeError(rc, "moe_shard_range")
     return s.value, n.value
+
+
+def quantize_mxfp4(src_ptr: int, n_elems: int, codes_ptr: int, scales_ptr: int, stream: int = 0):
+    """Device pointers: fp32 [n] -> e2m1 codes [ceil(n/32)*16] and E8M0 scales [ceil(n/32)]."""
+    rc = lib().moe_quantize_mxfp4(C.c_void_p(src_ptr), n_elems, C.c_void_p(codes_ptr), C.c_void_p(scales_ptr),
+                                  C.c_void_p(stream))
+    if rc != MOE_OK:
+        raise MoeError(rc, "moe_quantize_mxfp4")
 
 
 class PinnedBuffer:
@@ -179,6 +190,12 @@ class MoeBlock:
                                             out.ctypes.data_as(C.c_void_p), flags))
         self.rows = rows
         return out
+
+    def load_layer_f32(self, layer: int, w1: np.ndarray, b1: np.ndarray, w2: np.ndarray, b2: np.ndarray,
+                       router_w: np.ndarray, router_b: np.ndarray):
+        """fp32 expert tensors (w1 [E,2D,H], b1 [E,2D], w2 [E,H,D], b2 [E,H]) quantised to MXFP4 on the GPU."""
+        arrs = [np.ascontiguousarray(a, dtype=np.float32) for a in (w1, b1, w2, b2, router_w, router_b)]
+        self._check(self.L.moe_load_layer_f32(self.h, layer, *[a.ctypes.data_as(C.c_void_p) for a in arrs]))
 
     def forward_host_submit(self, layer: int, t_bits: np.ndarray, out: np.ndarray, flags: int = 0) -> int:
         """Starts one batch (host arrays, ideally PinnedBuffer.array, kept alive until the wait) and returns

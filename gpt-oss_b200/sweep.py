@@ -1,6 +1,7 @@
 """Secondary measurements of the MoE block (bench.py stays the headline).
 
     python -m gpt-oss_b200.sweep tokens [--zipf 1.2]     one GPU: rows in {1, 32, 256, 1856, 8192}
+    python -m gpt-oss_b200.sweep quantizer               one GPU: fp32 -> MXFP4 of 2^28 values (1 GiB), GB/s
     torchrun --nproc-per-node N -m gpt-oss_b200.sweep collectives
                                                           N GPUs: all-gather / reduce-scatter of bf16
                                                           [T, 2880], T in {64, 256, 1536, 1856, 8192},
@@ -71,6 +72,33 @@ def sweep_tokens(args):
     blk.close()
 
 
+def sweep_quantizer(args):
+    """The load-time quantiser alone: 4 bytes read and 17/32 byte written per element."""
+    import torch
+    pkg = importlib.import_module("gpt-oss_b200")
+    hbm, _ = _peaks()
+    n = 1 << 28
+    src = torch.randn(n, device="cuda", dtype=torch.float32)
+    codes = torch.empty(n // 2, dtype=torch.uint8, device="cuda")
+    scales = torch.empty(n // 32, dtype=torch.uint8, device="cuda")
+    stream = torch.cuda.current_stream()
+    run = lambda: pkg.quantize_mxfp4(src.data_ptr(), n, codes.data_ptr(), scales.data_ptr(), stream.cuda_stream)
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        run()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    nbytes = n * 4 + n // 2 + n // 32
+    print(json.dumps({"case": "quantizer", "elements": n, "ms": ms, "algorithmic_bytes": nbytes,
+                      "achieved_gbs": nbytes / ms / 1e6, "hbm_peak_gbs": hbm,
+                      "frac_of_measured_hbm": nbytes / ms / 1e6 / hbm}), flush=True)
+
+
 def sweep_collectives(args):
     import torch
     import torch.distributed as dist
@@ -129,14 +157,16 @@ def sweep_collectives(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["tokens", "collectives"])
+    ap.add_argument("what", choices=["tokens", "collectives", "quantizer"])
     ap.add_argument("--zipf", type=float, default=None)
     ap.add_argument("--rows", default=None)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--experts", type=int, default=128, help="tokens: experts of the layer (32 = the 20B shape)")
     args = ap.parse_args()
     sys.path.insert(0, ROOT)
-    if args.what == "tokens":
+    if args.what == "quantizer":
+        sweep_quantizer(args)
+    elif args.what == "tokens":
         args.rows = args.rows or "1,32,256,1856,8192"
         sweep_tokens(args)
     else:

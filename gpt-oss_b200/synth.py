@@ -97,6 +97,40 @@ def make_residual(n_tokens: int, hidden: int, seed: int = 0) -> tuple[np.ndarray
     return f32_to_bf16_bits(x), f32_to_bf16_bits(gain)
 
 
+def make_quantizer_inputs(seed: int = 0) -> np.ndarray:
+    """fp32 values that exercise the MXFP4 quantiser: wide-range random blocks, an all-zero block, values
+    exactly midway between two E2M1 magnitudes, signed zeros, denormals, values near the float maximum,
+    block maxima that are exact powers of two or just below one, values above 6 x scale, and a ragged
+    tail (the length is not a multiple of 32)."""
+    rng = np.random.Generator(np.random.Philox([seed, 0x717561]))
+    parts = []
+    body = rng.standard_normal(32 * 64).astype(np.float32)
+    body *= np.repeat(np.exp2(rng.integers(-30, 30, size=64)).astype(np.float32), 32)
+    parts.append(body)
+    parts.append(np.zeros(32, dtype=np.float32))
+    mids = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 7.0, 7.99], dtype=np.float32)
+    for k in (-3, 0, 5):
+        blk = np.zeros(32, dtype=np.float32)
+        blk[:9] = mids * np.float32(2.0 ** k)
+        blk[9:18] = -mids * np.float32(2.0 ** k)
+        blk[18] = np.float32(4.0 * 2.0 ** k)          # fixes the block exponent at k
+        blk[19] = np.float32(-0.0)
+        parts.append(blk)
+    tiny = np.full(32, np.float32(1e-41), dtype=np.float32)     # denormals
+    tiny[5] = np.float32(3e-39)
+    parts.append(tiny)
+    huge = rng.uniform(-3e38, 3e38, size=32).astype(np.float32)
+    parts.append(huge)
+    pow2 = rng.uniform(-1, 1, size=32).astype(np.float32)
+    pow2[7] = np.float32(8.0)
+    parts.append(pow2)
+    below = rng.uniform(-1, 1, size=32).astype(np.float32)
+    below[3] = np.nextafter(np.float32(8.0), np.float32(0.0))
+    parts.append(below)
+    parts.append(rng.standard_normal(13).astype(np.float32))    # ragged tail
+    return np.concatenate(parts)
+
+
 def weight_bytes_per_expert(hidden: int, inter: int) -> int:
     """MXFP4 codes + E8M0 scales + bf16 biases of one expert (both MLPs)."""
     w1 = 2 * inter * hidden

@@ -92,6 +92,25 @@ int moe_shard_range(int intermediate_dim, int tp_size, int tp_rank, int *start, 
 int moe_forward(moe_handle h, int layer, const void *t_dev, int rows, void *out_dev, unsigned flags,
                 void *stream);
 
+/* fp32 -> MXFP4 on the device: replaces a launch of quantize_pack_mxfp4_block32_kernel
+ * (getp-csrc/memory/mxfp4.hpp:139-217; launched at getp_run.cpp:1210, :1433).  Per 32 consecutive
+ * elements one E8M0 byte (ilogb of the block maximum minus 2, plus 127) and 16 bytes of e2m1 codes
+ * (low nibble = even element), bit-identical to the reference's.  codes_dev: ceil(n/32)*16 bytes,
+ * scales_dev: ceil(n/32) bytes; elements past n count as 0; codes_dev must be 4-byte aligned.
+ * Stream-ordered on the current device, no handle needed. */
+int moe_quantize_mxfp4(const float *src_dev, size_t n_elems, uint8_t *codes_dev, uint8_t *scales_dev,
+                       void *stream);
+
+/* moe_load_layer for an fp32 checkpoint (layout of run.cpp:206-247: w_mlp1 [E, 2D, H], b_mlp1 [E, 2D],
+ * w_mlp2 [E, H, D], b_mlp2 [E, H], all fp32, host pointers to the layer's tensors): replaces
+ * streaming_quantize_copy_mxfp4_cpu_to_gpu (getp_run.cpp:1104-1245) and the MoE part of
+ * copy_weights_to_gpu_120b (:1480-1718).  The expert weights are quantised on the GPU in chunks
+ * and the biases rounded to bf16, then loaded as by moe_load_layer.  The whole tensors are
+ * quantised before the TP shard is cut; the reference quantises each shard, which gives different
+ * MXFP4 blocks where a shard of the intermediate dimension does not start on a multiple of 32. */
+int moe_load_layer_f32(moe_handle h, int layer, const float *w1, const float *b1, const float *w2,
+                       const float *b2, const float *router_w, const float *router_b);
+
 /* Replaces moe_gpu()/moe_gpu_120b() as a whole (getp_run.cpp:2540, :2896), steps 0-10: the residual
  * stream rows x_dev (bf16 [rows_local, H], this rank's rows) are RMS-normalised with the bf16 gain
  * rms_w_dev [H] (rmsnorm_kernel_bf16_io, kernels/rmsnorm.hpp:115-164), go through the block (through

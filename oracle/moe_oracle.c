@@ -6,8 +6,9 @@
  *
  * Pinning: tests/test_oracle.py compares this file, on seeded inputs, with
  * the reference's own forward() (run.cpp compiled unmodified into
- * oracle/_ref/libref_moe.so by oracle/Makefile) and with the committed
- * outputs of that binary under tests/golden/.
+ * oracle/_ref/libref_moe.so by oracle/Makefile), with the reference's own
+ * quantiser source run on host threads (oracle/_ref/libref_mxfp4.so), and with
+ * the committed outputs of those binaries under tests/golden/.
  *
  * Every function names the reference lines it restates (paths are relative to
  * the reference project root).  The arithmetic keeps the reference's exact
@@ -255,6 +256,63 @@ int oracle_moe_layer(const float *t, int T, int H, int D, int E, int K,
   return oracle_moe_layer_shard(t, T, H, D, E, K, limit, w1c, w1s, b1, w2c,
                                 w2s, b2, wr, br, 0, D, 1, logits, topk_i,
                                 topk_v, out);
+}
+
+/*
+ * The reference's load-time quantiser, getp-csrc/memory/mxfp4.hpp:113-131
+ * (encode helpers) and :139-217 (quantize_pack_mxfp4_block32_kernel): per 32
+ * consecutive elements, exp = ilogb(max|v|) - 2 (0 for an all-zero block), the
+ * scale byte is exp + 127 clamped to [0, 255], every element is divided by
+ * 2^exp (the unclamped one) and takes the FIRST of the 16 table entries at the
+ * smallest distance (strict '<' while scanning codes 0..15, so a value midway
+ * between two magnitudes keeps the smaller one and -0.0 never wins over +0.0);
+ * elements past n count as 0; low nibble = even element.
+ * codes: ceil(n/32)*16 bytes, scales: ceil(n/32) bytes.
+ */
+void oracle_mxfp4_quantize(const float *src, size_t n, uint8_t *codes,
+                           uint8_t *scales) {
+  const size_t nblk = (n + 31) / 32;
+#pragma omp parallel for schedule(static)
+  for (size_t b = 0; b < nblk; ++b) {
+    float v[32];
+    float maxabs = 0.f;
+    for (int i = 0; i < 32; ++i) {
+      const size_t g = b * 32 + (size_t)i;
+      v[i] = g < n ? src[g] : 0.0f;
+      const float a = fabsf(v[i]);
+      if (a > maxabs)
+        maxabs = a;
+    }
+    int exp_scale = 0;
+    if (maxabs > 0.f) {
+      int e;
+      frexpf(maxabs, &e);
+      exp_scale = (e - 1) - 2;
+    }
+    int eb = exp_scale + 127;
+    if (eb < 0)
+      eb = 0;
+    if (eb > 255)
+      eb = 255;
+    scales[b] = (uint8_t)eb;
+    const float X = ldexpf(1.0f, exp_scale);
+    uint8_t nib[32];
+    for (int i = 0; i < 32; ++i) {
+      const float x = v[i] / X;
+      uint8_t best = 0;
+      float best_diff = fabsf(x - ORACLE_E2M1_LUT[0]);
+      for (uint8_t c = 1; c < 16; ++c) {
+        const float d = fabsf(x - ORACLE_E2M1_LUT[c]);
+        if (d < best_diff) {
+          best_diff = d;
+          best = c;
+        }
+      }
+      nib[i] = best;
+    }
+    for (int i = 0; i < 16; ++i)
+      codes[b * 16 + i] = (uint8_t)((nib[2 * i + 1] << 4) | (nib[2 * i] & 0xF));
+  }
 }
 
 /* Round-to-nearest-even float -> bf16 -> float (finite inputs). */

@@ -22,6 +22,7 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 PORT_SO = os.path.join(HERE, "libmoe_oracle.so")
 REF_SO = os.path.join(HERE, "_ref", "libref_moe.so")
+REF_MXFP4_SO = os.path.join(HERE, "_ref", "libref_mxfp4.so")
 
 
 def build(quiet: bool = True) -> None:
@@ -71,6 +72,17 @@ class Port:
         self.lib.oracle_mxfp4_dequant(_ptr(codes, C.c_uint8), _ptr(scales, C.c_uint8),
                                       C.c_size_t(out.size), _ptr(out, C.c_float))
         return out
+
+    def quantize(self, values: np.ndarray):
+        """fp32 values (flattened) -> (codes uint8 [ceil(n/32)*16], scales uint8 [ceil(n/32)])."""
+        v = np.ascontiguousarray(values, dtype=np.float32).reshape(-1)
+        nblk = (v.size + 31) // 32
+        codes = np.empty(nblk * 16, dtype=np.uint8)
+        scales = np.empty(nblk, dtype=np.uint8)
+        self.lib.oracle_mxfp4_quantize.restype = None
+        self.lib.oracle_mxfp4_quantize(_ptr(v, C.c_float), C.c_size_t(v.size), _ptr(codes, C.c_uint8),
+                                       _ptr(scales, C.c_uint8))
+        return codes, scales
 
     def topk_softmax(self, logits: np.ndarray, k: int = 4):
         logits = np.ascontiguousarray(logits, dtype=np.float32)
@@ -134,6 +146,43 @@ class Port:
 
 def reference_available() -> bool:
     return os.path.exists(REF_SO)
+
+
+def reference_quantizer_available() -> bool:
+    return os.path.exists(REF_MXFP4_SO)
+
+
+class ReferenceQuantizer:
+    """The reference's own MXFP4 quantiser and decoder (getp-csrc/memory/mxfp4.hpp:41-57, :113-217),
+    its kernel body run on 32 host threads."""
+
+    def __init__(self):
+        if not os.path.exists(REF_MXFP4_SO):
+            build()
+        if not os.path.exists(REF_MXFP4_SO):
+            raise FileNotFoundError(REF_MXFP4_SO)
+        self.lib = C.CDLL(REF_MXFP4_SO)
+        self.lib.ref_mxfp4_quantize.restype = C.c_int
+        self.lib.ref_mxfp4_dequantize.restype = None
+
+    def quantize(self, values: np.ndarray):
+        v = np.ascontiguousarray(values, dtype=np.float32).reshape(-1)
+        nblk = (v.size + 31) // 32
+        codes = np.empty(nblk * 16, dtype=np.uint8)
+        scales = np.empty(nblk, dtype=np.uint8)
+        rc = self.lib.ref_mxfp4_quantize(_ptr(v, C.c_float), C.c_size_t(v.size), _ptr(codes, C.c_uint8),
+                                         _ptr(scales, C.c_uint8))
+        if rc != 0:
+            raise RuntimeError(f"ref_mxfp4_quantize failed: {rc}")
+        return codes, scales
+
+    def dequantize(self, codes: np.ndarray, scales: np.ndarray, n: int) -> np.ndarray:
+        codes = np.ascontiguousarray(codes, dtype=np.uint8)
+        scales = np.ascontiguousarray(scales, dtype=np.uint8)
+        out = np.empty(n, dtype=np.float32)
+        self.lib.ref_mxfp4_dequantize(_ptr(codes, C.c_uint8), _ptr(scales, C.c_uint8), C.c_size_t(n),
+                                      _ptr(out, C.c_float))
+        return out
 
 
 class Reference:

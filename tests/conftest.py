@@ -39,7 +39,8 @@ GOLDEN_DIR = os.path.join(ROOT, "tests", "golden")
 
 
 def golden_cases():
-    return sorted(f[:-4] for f in os.listdir(GOLDEN_DIR) if f.endswith(".npz") and not f.startswith("block_"))
+    return sorted(f[:-4] for f in os.listdir(GOLDEN_DIR)
+                  if f.endswith(".npz") and not f.startswith(("block_", "quant_")))
 
 
 def golden_block_cases():

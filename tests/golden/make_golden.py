@@ -85,6 +85,14 @@ def main():
         path = os.path.join(here, name + ".npz")
         np.savez_compressed(path, **blob)
         print(f"{name}: {os.path.getsize(path)} bytes, e_agg rms {np.sqrt((agg ** 2).mean()):.4f}")
+    # the reference's own MXFP4 quantiser (getp-csrc/memory/mxfp4.hpp:113-217) on edge-case inputs
+    vals = synth.make_quantizer_inputs(seed=1)
+    q = oracle.ReferenceQuantizer()
+    codes, scales = q.quantize(vals)
+    back = q.dequantize(codes, scales, vals.size)
+    path = os.path.join(here, "quant_edge_cases.npz")
+    np.savez_compressed(path, values=vals, codes=codes, scales=scales, dequant=back)
+    print(f"quant_edge_cases: {os.path.getsize(path)} bytes, {vals.size} values")
 
 
 if __name__ == "__main__":

@@ -128,3 +128,37 @@ def test_block_with_rmsnorm_matches_reference_live(synth, port):
     p = port.moe_block(layer, x, gain)
     for a, b in zip(p[:5], r):
         assert np.array_equal(a, b)
+
+
+def test_quantizer_matches_reference_golden(synth, port):
+    """The MXFP4 quantiser restatement against committed outputs of the reference's own source
+    (getp-csrc/memory/mxfp4.hpp:113-217), bit for bit, and the decode of those bytes."""
+    z = np.load(os.path.join(GOLDEN_DIR, "quant_edge_cases.npz"))
+    vals = synth.make_quantizer_inputs(seed=1)
+    assert np.array_equal(vals.view(np.uint32), z["values"].view(np.uint32)), "generator drifted from the fixture"
+    codes, scales = port.quantize(vals)
+    assert np.array_equal(codes, z["codes"]) and np.array_equal(scales, z["scales"])
+    n = vals.size
+    pad = (-n) % 32
+    back = port.dequant(codes.reshape(-1, 16), scales.reshape(-1, 1)).reshape(-1)[:n]
+    # Scale byte 0 (only the block of denormals reaches it, through the clamp) is the one encoding the two
+    # decoders read differently: the reference forms the scale by a shift into the exponent field
+    # (mxfp4.hpp:53), which gives 0 there, where E8M0 means 2^-127.
+    live = np.repeat(scales != 0, 32)[:n]
+    assert (~live).sum() == 32
+    assert np.array_equal(back.view(np.uint32)[live], z["dequant"].view(np.uint32)[live])
+    # the quantisation error is bounded by half the coarsest step (1 x scale above 4, clipping at 6)
+    sc = np.repeat(np.exp2(scales.astype(np.float64) - 127), 32)[:n]
+    inside = (np.abs(vals) <= 6 * sc) & live
+    assert (np.abs(back.astype(np.float64) - vals)[inside] <= 1.0 * sc[inside]).all()
+    assert pad == 19
+
+
+@pytest.mark.skipif(not oracle.reference_quantizer_available(), reason="oracle/_ref/libref_mxfp4.so not built")
+def test_quantizer_matches_reference_live(port):
+    rng = np.random.default_rng(7)
+    v = (rng.standard_normal(32 * 300 + 5) * np.exp(rng.uniform(-20, 20, 32 * 300 + 5))).astype(np.float32)
+    ref = oracle.ReferenceQuantizer()
+    rc, rs = ref.quantize(v)
+    pc, ps = port.quantize(v)
+    assert np.array_equal(pc, rc) and np.array_equal(ps, rs)
