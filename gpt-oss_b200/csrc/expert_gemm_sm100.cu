@@ -126,6 +126,7 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     if (lane == 0) {
       uint32_t it = 0, item = 0;
       bool ok = true;
+      const uint64_t w_policy = l2_policy_evict_first();
       WorkItem w_next = {};
       if (static_cast<int>(blockIdx.x) < n_work) w_next = p.work[blockIdx.x];
       for (int wi = blockIdx.x; ok && wi < n_work; wi += gridDim.x) {
@@ -146,9 +147,10 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
           const uint32_t stage = smem_base + s * kStageBytes;
           mbar_arrive_expect_tx(full_bar(s), kABytes + kWLoadBytes + kSfbChunkBytes);
           tma_load_2d(stage, &tm_x, kc * kChunkK, w.tile * kTileM, full_bar(s));
-          tma_load_3d(stage + kABytes, &tm_w, 0, 0, static_cast<int>(tile0 + kc), full_bar(s));
-          bulk_load(stage + kABytes + kWBytes, p.w_tiles + static_cast<size_t>(tile0 + kc) * kWTileStride + kWTileCodes,
-                    kSfbChunkBytes, full_bar(s));
+          // weights pass through once per step: they must not push the activations and the results out of L2
+          tma_load_3d_hint(stage + kABytes, &tm_w, 0, 0, static_cast<int>(tile0 + kc), full_bar(s), w_policy);
+          bulk_load_hint(stage + kABytes + kWBytes, p.w_tiles + static_cast<size_t>(tile0 + kc) * kWTileStride + kWTileCodes,
+                         kSfbChunkBytes, full_bar(s), w_policy);
         }
        }
       }

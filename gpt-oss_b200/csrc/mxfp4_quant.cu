@@ -8,9 +8,10 @@
 // to the reference's: same block maximum, same exponent rule, same first-best
 // scan of the 16 table entries.
 //
-// One warp per 32-element block (the reference's "logical warp"), warp
-// shuffles instead of its shared-memory staging; a grid-stride loop over the
-// blocks of the call.  HBM-bound: 4 bytes read and 17/32 byte written per
+// Four lanes per 32-element block (the reference gives it a "logical warp" of
+// 32), shuffles instead of its shared-memory staging, thresholds instead of its
+// 16-way scan, a multiplication by 2^-exp instead of its division; a grid-stride
+// loop over the blocks of the call.  HBM-bound: 4 bytes read and 17/32 byte written per
 // element.
 #include <cstdarg>
 #include <cstdio>
@@ -20,46 +21,76 @@
 
 namespace moe {
 
-__constant__ float kE2m1Lut[16] = {0.0f,  0.5f,  1.0f,  1.5f,  2.0f,  3.0f,  4.0f,  6.0f,
-                                   -0.0f, -0.5f, -1.0f, -1.5f, -2.0f, -3.0f, -4.0f, -6.0f};
+// Code of x (already divided by the block scale).  The reference scans the 16 table entries in order and
+// keeps the first at the smallest distance (mxfp4.hpp:121-131).  That is: the nearest magnitude of
+// {0, .5, 1, 1.5, 2, 3, 4, 6}, the smaller one at an exact midpoint (the distances there are exact in fp32,
+// so thresholds decide exactly as the scan does), the sign bit only with a non-zero magnitude (+0 precedes
+// -0 in the table), and code 0 for NaN and for infinities (no distance is smaller than the first, infinite one).
+__device__ __forceinline__ uint32_t e2m1_first_nearest(float x) {
+  const float a = fabsf(x);
+  uint32_t idx = (a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) + (a > 3.5f) + (a > 5.0f);
+  if (!(a < __int_as_float(0x7f800000))) idx = 0;
+  return (x < 0.f && idx != 0) ? (idx | 8u) : idx;
+}
 
+// Four lanes per 32-element block, eight consecutive elements per lane (two 16-byte loads in flight).
 __global__ void __launch_bounds__(256)
 mxfp4_quantize_kernel(const float *__restrict__ src, size_t n, uint8_t *__restrict__ codes,
                       uint8_t *__restrict__ scales, size_t n_blocks) {
   const int lane = threadIdx.x & 31;
-  const size_t warps = (static_cast<size_t>(gridDim.x) * blockDim.x) >> 5;
-  for (size_t b = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; b < n_blocks; b += warps) {
-    const size_t g = b * 32 + lane;
-    const float v = g < n ? src[g] : 0.0f;  // elements past the end count as 0 (mxfp4.hpp:170-174)
+  const size_t total = n_blocks * 4;  // 8-element groups, the last block padded with zeros
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  const bool vec_ok = (reinterpret_cast<uintptr_t>(src) & 15u) == 0;
+  for (size_t base = static_cast<size_t>(blockIdx.x) * blockDim.x + (threadIdx.x & ~31); base < total; base += stride) {
+    const size_t q = base + lane, g0 = q * 8;
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // elements past the end count as 0 (mxfp4.hpp:170-174)
+    if (q < total) {
+      if (vec_ok && g0 + 7 < n) {
+        const float4 f0 = __ldg(reinterpret_cast<const float4 *>(src + g0));
+        const float4 f1 = __ldg(reinterpret_cast<const float4 *>(src + g0) + 1);
+        v[0] = f0.x; v[1] = f0.y; v[2] = f0.z; v[3] = f0.w;
+        v[4] = f1.x; v[5] = f1.y; v[6] = f1.z; v[7] = f1.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (g0 + j < n) v[j] = src[g0 + j];
+      }
+    }
     // largest |v| of the block; a NaN never wins a '>' in the reference's scan, fmaxf drops it the same way
-    float maxabs = fabsf(v);
-    if (!(maxabs == maxabs)) maxabs = 0.f;
+    float maxabs = 0.f;
 #pragma unroll
-    for (int off = 16; off; off >>= 1) maxabs = fmaxf(maxabs, __shfl_xor_sync(0xffffffffu, maxabs, off));
+    for (int j = 0; j < 8; ++j) maxabs = fmaxf(maxabs, fabsf(v[j]));
+    maxabs = fmaxf(maxabs, __shfl_xor_sync(0xffffffffu, maxabs, 1));
+    maxabs = fmaxf(maxabs, __shfl_xor_sync(0xffffffffu, maxabs, 2));
+    // exp = ilogb(maxabs) - 2 (the largest power of two among the E2M1 magnitudes is 2^2), 0 for a zero block
+    const uint32_t mbits = __float_as_uint(maxabs);
     int exp_scale = 0;
-    if (maxabs > 0.f) {
-      int e;
-      frexpf(maxabs, &e);
-      exp_scale = (e - 1) - 2;  // the largest power of two among the E2M1 magnitudes is 2^2
-    }
-    if (lane == 0) scales[b] = static_cast<uint8_t>(min(max(exp_scale + 127, 0), 255));
-    const float x = v / ldexpf(1.0f, exp_scale);
-    // first of the 16 entries at the smallest distance (mxfp4.hpp:121-131)
-    uint32_t best = 0;
-    float best_diff = fabsf(x - kE2m1Lut[0]);
+    float x[8];
+    if (mbits >= 0x01800000u && mbits < 0x7f800000u) {
+      // maximum of at least 2^-124: the exponent field is ilogb, and 2^-exp is a normal float, so multiplying
+      // by it rounds exactly as the reference's division by 2^exp does
+      exp_scale = static_cast<int>(mbits >> 23) - 127 - 2;
+      const float inv = __uint_as_float(static_cast<uint32_t>(127 - exp_scale) << 23);
 #pragma unroll
-    for (uint32_t c = 1; c < 16; ++c) {
-      const float d = fabsf(x - kE2m1Lut[c]);
-      if (d < best_diff) { best_diff = d; best = c; }
+      for (int j = 0; j < 8; ++j) x[j] = v[j] * inv;
+    } else {
+      if (maxabs > 0.f) {  // tiny or infinite maximum: the reference's own library calls
+        int e;
+        frexpf(maxabs, &e);
+        exp_scale = (e - 1) - 2;
+      }
+      const float X = ldexpf(1.0f, exp_scale);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = v[j] / X;
     }
-    // low nibble = even element; lane 4j gathers the byte quartet j
-    const uint32_t hi = __shfl_down_sync(0xffffffffu, best, 1);
-    const uint32_t byte = (hi << 4) | best;            // valid on even lanes
-    const uint32_t b1 = __shfl_down_sync(0xffffffffu, byte, 2);
-    const uint32_t b2 = __shfl_down_sync(0xffffffffu, byte, 4);
-    const uint32_t b3 = __shfl_down_sync(0xffffffffu, byte, 6);
-    if ((lane & 7) == 0)
-      reinterpret_cast<uint32_t *>(codes + b * 16)[lane >> 3] = byte | (b1 << 8) | (b2 << 16) | (b3 << 24);
+    uint32_t word = 0;  // low nibble = even element
+#pragma unroll
+    for (int j = 0; j < 8; ++j) word |= e2m1_first_nearest(x[j]) << (4 * j);
+    if (q < total) {
+      const size_t b = q >> 2;
+      reinterpret_cast<uint32_t *>(codes + b * 16)[q & 3] = word;
+      if ((q & 3) == 0) scales[b] = static_cast<uint8_t>(min(max(exp_scale + 127, 0), 255));
+    }
   }
 }
 
@@ -91,7 +122,7 @@ uint16_t bf16_rn(float f) {
 
 void launch_quantize(const float *src, size_t n, uint8_t *codes, uint8_t *scales, cudaStream_t s) {
   const size_t n_blocks = (n + 31) / 32;
-  const size_t want = (n_blocks + 7) / 8;  // 8 warps per CTA
+  const size_t want = (n_blocks * 4 + 255) / 256;  // four lanes per block, 256 threads per CTA
   const unsigned grid = static_cast<unsigned>(std::min<size_t>(want, 148 * 16));
   mxfp4_quantize_kernel<<<std::max(grid, 1u), 256, 0, s>>>(src, n, codes, scales, n_blocks);
 }

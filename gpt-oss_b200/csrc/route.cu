@@ -277,7 +277,8 @@ void launch_topk_softmax(float *logits, const float *partial, int splits, const 
 __global__ void __launch_bounds__(256)
 build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ counts, int T, int E, int K,
                    int n_ntiles1, int n_ntiles2, int *__restrict__ offsets, int *__restrict__ tile_base,
-                   int *__restrict__ pair_row, int *__restrict__ row_token, WorkItem *__restrict__ work1,
+                   int *__restrict__ pair_row, int *__restrict__ row_token, int *__restrict__ row_slot,
+                   WorkItem *__restrict__ work1,
                    WorkItem *__restrict__ work2, int *__restrict__ n_work, int max_work1, int max_work2,
                    unsigned int *status) {
   __shared__ int s_red[2][8];
@@ -325,8 +326,11 @@ build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ cou
     for (int i = 0; i < warp; ++i) before += s_warp[i];
     if (hit >= 0) {
       const int r = off + before + __popc(m & ((1u << lane) - 1u));
-      if (before + __popc(m & ((1u << lane) - 1u)) < cnt) {
+      const int pos = before + __popc(m & ((1u << lane) - 1u));
+      if (pos < cnt) {
         row_token[r] = t;
+        // where the row's high term goes in the quantised activations: token tile, then 2 rows per token
+        row_slot[r] = (tiles_before + pos / kTokTile) * kTileM + 2 * (pos % kTokTile);
         pair_row[static_cast<size_t>(t) * K + hit] = r;
       } else {
         atomicOr(status, ST_BAD_INDEX);
@@ -368,11 +372,11 @@ build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ cou
 }
 
 void launch_build_index(const int *topk_idx, const int *counts, int T, int E, int K, int n_ntiles1, int n_ntiles2,
-                        int *offsets, int *tile_base, int *pair_row, int *row_token, WorkItem *work1,
-                        WorkItem *work2, int *n_work, int max_work1, int max_work2, unsigned int *status,
-                        cudaStream_t s) {
+                        int *offsets, int *tile_base, int *pair_row, int *row_token, int *row_slot,
+                        WorkItem *work1, WorkItem *work2, int *n_work, int max_work1, int max_work2,
+                        unsigned int *status, cudaStream_t s) {
   build_index_kernel<<<E, 256, 0, s>>>(topk_idx, counts, T, E, K, n_ntiles1, n_ntiles2, offsets, tile_base,
-                                       pair_row, row_token, work1, work2, n_work, max_work1, max_work2, status);
+                                       pair_row, row_token, row_slot, work1, work2, n_work, max_work1, max_work2, status);
 }
 
 // ---------------------------------------------------------------------------
@@ -388,26 +392,26 @@ void launch_build_index(const int *topk_idx, const int *counts, int T, int E, in
 // into the tile's 512-byte scale atom, byte (r%32)*16 + (r/32)*4 + kb for row r
 // and every k block kb (the scale is per row, so the four bytes are equal).
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(128)
+constexpr int kQrThreads = 128, kQrVec = 4;   // a row of up to 128*4*8 = 4096 elements stays in registers
+
+__global__ void __launch_bounds__(kQrThreads)
 quantize_rows_kernel(const __nv_bfloat16 *__restrict__ t, const int *__restrict__ row_token,
-                     const int *__restrict__ offsets, const int *__restrict__ tile_base, int E,
+                     const int *__restrict__ row_slot, const int *__restrict__ n_rows,
                      uint8_t *__restrict__ xq, uint8_t *__restrict__ sfa, int H) {
-  __shared__ float s_max[4];
+  __shared__ float s_max[kQrThreads / 32];
   const int r = blockIdx.x;
-  if (r >= offsets[E]) return;
-  int lo = 0, hi = E;  // expert of this permuted row: offsets[lo] <= r < offsets[hi]
-  while (hi - lo > 1) {
-    const int mid = (lo + hi) >> 1;
-    if (offsets[mid] <= r) lo = mid; else hi = mid;
-  }
-  const int pos = r - offsets[lo];
-  const int tile = tile_base[lo] + pos / kTokTile, i = pos % kTokTile;
-  const int tok = row_token[r];
+  if (r >= *n_rows) return;
+  const int tok = row_token[r], slot = row_slot[r];
+  const int tile = slot / kTileM, i2 = slot % kTileM;   // i2 = 2 * (token's place in the tile)
   const uint4 *src = reinterpret_cast<const uint4 *>(t + static_cast<size_t>(tok) * H);
+  const int nvec = H / 8;
+  uint4 v[kQrVec];
   float amax = 0.f;
-  for (int c = threadIdx.x; c < H / 8; c += blockDim.x) {
-    const uint4 v = __ldg(src + c);
-    const uint32_t in[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int u = 0; u < kQrVec; ++u) {
+    const int c = threadIdx.x + u * kQrThreads;
+    v[u] = c < nvec ? __ldg(src + c) : make_uint4(0u, 0u, 0u, 0u);
+    const uint32_t in[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       amax = fmaxf(amax, fabsf(__uint_as_float(in[j] << 16)));
@@ -423,11 +427,13 @@ quantize_rows_kernel(const __nv_bfloat16 *__restrict__ t, const int *__restrict_
   int e = static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu) - 127 - 7;
   e = max(-120, min(e, 120));
   const float inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);  // 2^-e
-  uint8_t *row_hi = xq + (static_cast<size_t>(tile) * kTileM + 2 * i) * H;
+  uint8_t *row_hi = xq + (static_cast<size_t>(tile) * kTileM + i2) * H;
   uint8_t *row_lo = row_hi + H;
-  for (int c = threadIdx.x; c < H / 8; c += blockDim.x) {
-    const uint4 v = __ldg(src + c);
-    const uint32_t in[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int u = 0; u < kQrVec; ++u) {
+    const int c = threadIdx.x + u * kQrThreads;
+    if (c >= nvec) break;
+    const uint32_t in[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
     float f[8];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -454,16 +460,18 @@ quantize_rows_kernel(const __nv_bfloat16 *__restrict__ t, const int *__restrict_
     reinterpret_cast<uint2 *>(row_lo)[c] = make_uint2(l8[0], l8[1]);
   }
   if (threadIdx.x < 2) {
-    const int rr = 2 * i + threadIdx.x;  // row inside the tile: even = high, odd = low
+    const int rr = i2 + threadIdx.x;  // row inside the tile: even = high, odd = low
     const uint32_t byte = static_cast<uint32_t>(127 + e - 4 * static_cast<int>(threadIdx.x));
     uint8_t *atom = sfa + static_cast<size_t>(tile) * kSfAtomBytes;
     *reinterpret_cast<uint32_t *>(atom + (rr % 32) * 16 + (rr / 32) * 4) = byte * 0x01010101u;
   }
 }
 
-void launch_quantize_rows(const __nv_bfloat16 *t, const int *row_token, const int *offsets, const int *tile_base,
-                          int E, uint8_t *xq, uint8_t *sfa, int H, int n_rows, cudaStream_t s) {
-  quantize_rows_kernel<<<n_rows, 128, 0, s>>>(t, row_token, offsets, tile_base, E, xq, sfa, H);
+int quantize_rows_max_hidden() { return kQrThreads * kQrVec * 8; }
+
+void launch_quantize_rows(const __nv_bfloat16 *t, const int *row_token, const int *row_slot, const int *n_rows_dev,
+                          uint8_t *xq, uint8_t *sfa, int H, int n_rows, cudaStream_t s) {
+  quantize_rows_kernel<<<n_rows, kQrThreads, 0, s>>>(t, row_token, row_slot, n_rows_dev, xq, sfa, H);
 }
 
 // ---------------------------------------------------------------------------

@@ -373,3 +373,35 @@ def test_host_pipeline_submit_wait(pkg, synth):
             p.free()
     finally:
         blk.close()
+
+
+def test_forward_in_a_cuda_graph(pkg, synth):
+    """The per-layer call is stream-ordered work only (no allocation, no host synchronisation), so a caller
+    can capture it once and replay it per step (the reference launches every kernel of every layer from the
+    host, getp_run.cpp:3313-3367).  A replay on new rows gives the bits of a direct call."""
+    import torch
+    E, H, D, T = 16, 256, 320, 96
+    layer = synth.make_layer(E, H, D, seed=41)
+    a, b = synth.make_tokens(T, H, seed=42), synth.make_tokens(T, H, seed=43)
+    blk = pkg.MoeBlock(H, D, E, max_rows=T)
+    try:
+        blk.load_layer(0, layer)
+        want_a, want_b = blk.forward_host(0, a).copy(), blk.forward_host(0, b).copy()
+        d_t = torch.from_numpy(a.view(np.int16).copy()).cuda()
+        d_o = torch.zeros_like(d_t)
+        s = torch.cuda.Stream()
+        with torch.cuda.stream(s):
+            blk.forward(0, d_t.data_ptr(), T, d_o.data_ptr(), 0, s.cuda_stream)   # first call outside the capture
+        s.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            blk.forward(0, d_t.data_ptr(), T, d_o.data_ptr(), 0, torch.cuda.current_stream().cuda_stream)
+        for rows, want in ((a, want_a), (b, want_b), (a, want_a)):
+            d_t.copy_(torch.from_numpy(rows.view(np.int16).copy()))
+            d_o.zero_()
+            g.replay()
+            torch.cuda.synchronize()
+            assert np.array_equal(d_o.cpu().numpy().view(np.uint16), want)
+        blk.synchronize()
+    finally:
+        blk.close()
