@@ -20,7 +20,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("MOE_B200_LIB") or os.path.join(HERE, "libmoe_b200.so")
 
 MOE_OK = 0
-ERR_NAMES = {1: "INVALID", 2: "CUDA", 3: "NOMEM", 4: "TIMEOUT", 5: "SCALE_RANGE", 6: "STATE", 7: "NO_SM100"}
+ERR_NAMES = {1: "INVALID", 2: "CUDA", 3: "NOMEM", 4: "TIMEOUT", 5: "SCALE_RANGE", 6: "STATE", 7: "NO_SM100", 8: "Y_RANGE"}
 
 CFG_KEEP_F32_OUT = 1
 FWD_SIMT_GEMM = 1
@@ -281,7 +281,7 @@ class MoeBlock:
             DBG_LOGITS: ((T, E), np.float32), DBG_TOPK_IDX: ((T, K), np.int32), DBG_TOPK_W: ((T, K), np.float32),
             DBG_COUNTS: ((E,), np.int32), DBG_OFFSETS: ((E + 1,), np.int32), DBG_PAIR_ROW: ((T, K), np.int32),
             DBG_ROW_TOKEN: ((T * K,), np.int32), DBG_OUT_F32: ((T, H), np.float32),
-            DBG_STATUS: ((1,), np.uint32), DBG_YBUF: ((T * K, H), np.float32),
+            DBG_STATUS: ((1,), np.uint32), DBG_YBUF: ((T * K, H), np.float16),
             DBG_GATHER: ((T, H), np.uint16), DBG_TNORM: ((T // self.cfg.tp_size, H), np.uint16)}[which]
         out = np.empty(shape, dtype=dt)
         self._check(self.L.moe_get_debug(self.h, which, out.ctypes.data_as(C.c_void_p), out.nbytes))

@@ -78,7 +78,7 @@ simt_mlp1_kernel(const uint8_t *__restrict__ w_tiles, const uint8_t *__restrict_
 __global__ void __launch_bounds__(256)
 simt_mlp2_kernel(const uint8_t *__restrict__ w_tiles, const uint8_t *__restrict__ scales,
                  const __nv_bfloat16 *__restrict__ bias, int add_bias, const __half *__restrict__ h,
-                 const int *__restrict__ offsets, int E, int Dl, int H, float *__restrict__ y_out) {
+                 const int *__restrict__ offsets, int E, int Dl, int H, __half *__restrict__ y_out) {
   const int r = blockIdx.x;
   if (r >= offsets[E]) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -89,7 +89,7 @@ simt_mlp2_kernel(const uint8_t *__restrict__ w_tiles, const uint8_t *__restrict_
   float v = warp_dot_mxfp4(tile_row(w_tiles, e, i, H, Dl), scales + row * (Dl / 32), h + static_cast<size_t>(r) * Dl, Dl, lane);
   if (lane == 0) {
     if (add_bias) v += __bfloat162float(bias[row]);
-    y_out[static_cast<size_t>(r) * H + i] = v;
+    y_out[static_cast<size_t>(r) * H + i] = __float2half_rn(v);
   }
 }
 
@@ -101,7 +101,7 @@ void launch_simt_mlp1(const uint8_t *w_tiles, const uint8_t *scales_raw, const _
 }
 
 void launch_simt_mlp2(const uint8_t *w_tiles, const uint8_t *scales_raw, const __nv_bfloat16 *bias,
-                      int add_bias, const __half *h, const int *offsets, int E, int Dl, int H, float *y_out,
+                      int add_bias, const __half *h, const int *offsets, int E, int Dl, int H, __half *y_out,
                       int n_rows, cudaStream_t s) {
   dim3 grid(n_rows, (H + 7) / 8);
   simt_mlp2_kernel<<<grid, 256, 0, s>>>(w_tiles, scales_raw, bias, add_bias, h, offsets, E, Dl, H, y_out);

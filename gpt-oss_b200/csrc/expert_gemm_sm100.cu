@@ -73,7 +73,7 @@ __device__ __forceinline__ float e4m3_to_float(uint32_t byte) {
   return __half2float(*reinterpret_cast<const __half *>(&h));
 }
 
-template <int MODE>  // 1 = MLP1 (bias + SwiGLU -> e4m3 high/low rows), 2 = MLP2 (bias -> fp32)
+template <int MODE>  // 1 = MLP1 (bias + SwiGLU -> e4m3 high/low rows), 2 = MLP2 (bias -> fp16)
 __global__ void __launch_bounds__(kThreads, 1)
 expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                    const GemmArgs p) {
@@ -238,14 +238,12 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 
       auto process = [&](const uint32_t (&v)[16], int c0) {
         // Sum of the high and low partial products of a token (adjacent lanes).  Each lane of the pair keeps 8
-        // of the 16 columns.  MLP1: even lane columns 0-7, odd lane 8-15 (whole gate/up pairs, 4 outputs each).
-        // MLP2: even lane columns 0-3 and 8-11, odd lane 4-7 and 12-15, so that the pair's two 16-byte stores
-        // of one instruction fill one 32-byte sector.
+        // of the 16 columns: the even lane columns 0-7, the odd lane 8-15 (MLP1: whole gate/up pairs, 4 outputs
+        // each; MLP2: 8 fp16 values, one 16-byte store, the pair's two stores fill one 32-byte sector).
         float tot[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          const int ce = (MODE == 1) ? i : (i < 4 ? i : i + 4);   // column the even lane keeps
-          const int co = (MODE == 1) ? i + 8 : ce + 4;            // column the odd lane keeps
+          const int ce = i, co = i + 8;   // columns the even / the odd lane keeps
           const float fe = __uint_as_float(v[ce]), fo = __uint_as_float(v[co]);
           const float mine = odd ? fo : fe;
           const float give = odd ? fe : fo;
@@ -282,13 +280,12 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             *reinterpret_cast<uint32_t *>(dst + p.ld_out) = lo4;
           }
         } else {
-          const int na = n0 + c0 + 4 * odd;  // this lane's columns: na..na+3 and na+8..na+11
+          const int na = n0 + c0 + 8 * odd;  // first of this lane's 8 columns
           if (tok_ok && na < p.R) {          // R is a multiple of 32 here, so the whole chunk is inside
             float b[8];
             if (p.add_bias) {
-              const uint2 b0 = __ldg(reinterpret_cast<const uint2 *>(bias_row + na));
-              const uint2 b1 = __ldg(reinterpret_cast<const uint2 *>(bias_row + na + 8));
-              const uint32_t bw[4] = {b0.x, b0.y, b1.x, b1.y};
+              const uint4 bv = __ldg(reinterpret_cast<const uint4 *>(bias_row + na));
+              const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
                 b[2 * i] = __uint_as_float(bw[i] << 16);
@@ -298,9 +295,20 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 #pragma unroll
               for (int i = 0; i < 8; ++i) b[i] = 0.f;
             }
-            float *dst = p.y_out + static_cast<size_t>(w.row0 + tok) * p.ld_out + na;
-            *reinterpret_cast<float4 *>(dst) = make_float4(tot[0] + b[0], tot[1] + b[1], tot[2] + b[2], tot[3] + b[3]);
-            *reinterpret_cast<float4 *>(dst + 8) = make_float4(tot[4] + b[4], tot[5] + b[5], tot[6] + b[6], tot[7] + b[7]);
+            // fp16 keeps 11 significant bits of a value that the combine will round to 8; what it cannot hold
+            // is a magnitude above 65504, which is reported, not stored silently as infinity
+            uint32_t o[4];
+            float big = 0.f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float y0 = tot[2 * i] + b[2 * i], y1 = tot[2 * i + 1] + b[2 * i + 1];
+              big = fmaxf(big, fmaxf(fabsf(y0), fabsf(y1)));
+              const __half2 hh = __floats2half2_rn(y0, y1);
+              o[i] = *reinterpret_cast<const uint32_t *>(&hh);
+            }
+            if (big > 65504.f) atomicOr(p.status, ST_Y_RANGE);
+            __half *dst = p.y_out + static_cast<size_t>(w.row0 + tok) * p.ld_out + na;
+            *reinterpret_cast<uint4 *>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
           }
         }
       };

@@ -257,6 +257,7 @@ const char *moe_strerror(int code) {
     case MOE_ERR_NOMEM: return "out of memory";
     case MOE_ERR_TIMEOUT: return "a bounded wait ran out";
     case MOE_ERR_SCALE_RANGE: return "E8M0 scale byte is NaN";
+    case MOE_ERR_Y_RANGE: return "an expert output does not fit fp16";
     case MOE_ERR_STATE: return "wrong state";
     case MOE_ERR_NO_SM100: return "device is not sm_100";
     default: return "unknown";
@@ -524,7 +525,7 @@ int moe_synchronize(moe_handle c) {
   CU_TRY(c, cudaMemcpy(&st, c->status, sizeof(st), cudaMemcpyDeviceToHost));
   if (st) {
     CU_TRY(c, cudaMemset(c->status, 0, sizeof(unsigned)));
-    return fail(c, (st & ST_BAD_INDEX) ? MOE_ERR_STATE : MOE_ERR_TIMEOUT, "device status word 0x%x", st);
+    return fail(c, status_error(st), "device status word 0x%x", st);
   }
   return MOE_OK;
 }
@@ -543,7 +544,7 @@ int moe_forward_host(moe_handle c, int layer, const void *t_host, int rows, void
   CU_TRY(c, cudaMemcpy(&st, c->status, sizeof(st), cudaMemcpyDeviceToHost));
   if (st) {
     CU_TRY(c, cudaMemset(c->status, 0, sizeof(unsigned)));
-    return fail(c, (st & ST_BAD_INDEX) ? MOE_ERR_STATE : MOE_ERR_TIMEOUT, "device status word 0x%x", st);
+    return fail(c, status_error(st), "device status word 0x%x", st);
   }
   return MOE_OK;
 }
@@ -574,7 +575,7 @@ int host_slot_finish(moe_ctx *c, HostSlot &hs) {
   const unsigned st = *hs.status_host;
   if (st) {
     CU_TRY(c, cudaMemset(c->status, 0, sizeof(unsigned)));
-    return fail(c, (st & ST_BAD_INDEX) ? MOE_ERR_STATE : MOE_ERR_TIMEOUT, "device status word 0x%x", st);
+    return fail(c, status_error(st), "device status word 0x%x", st);
   }
   return MOE_OK;
 }
@@ -674,7 +675,7 @@ int moe_get_debug(moe_handle c, int which, void *dst, size_t bytes) {
     case MOE_DBG_STATUS: src = c->status; have = 4096 * 4; break;
     case MOE_DBG_GATHER: src = c->t_in; have = static_cast<size_t>(c->max_rows) * c->H * 2; break;
     case MOE_DBG_TNORM: src = c->t_norm; have = static_cast<size_t>(c->max_rows) * c->H * 2; break;
-    case MOE_DBG_YBUF: src = c->ybuf; have = T * c->K * c->H * 4; break;
+    case MOE_DBG_YBUF: src = c->ybuf; have = T * c->K * c->H * 2; break;
     default: return fail(c, MOE_ERR_INVALID, "moe_get_debug: unknown item %d", which);
   }
   if (bytes > have) return fail(c, MOE_ERR_INVALID, "moe_get_debug: %zu bytes asked, %zu available", bytes, have);

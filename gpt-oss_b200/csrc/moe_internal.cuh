@@ -36,7 +36,13 @@ enum : unsigned {
   ST_WAIT_DEMPTY = 32u,   // expert GEMM: accumulator never drained
   ST_BAD_INDEX = 64u,     // routing produced an out-of-range row
   ST_WAIT_PEER = 128u,    // TP collective: a peer's flag never arrived
+  ST_Y_RANGE = 256u,      // expert GEMM: an MLP2 output does not fit fp16 (|y| > 65504)
 };
+
+// Error code for a non-zero device status word.
+inline int status_error(unsigned st) {
+  return (st & ST_BAD_INDEX) ? MOE_ERR_STATE : (st & ST_Y_RANGE) ? MOE_ERR_Y_RANGE : MOE_ERR_TIMEOUT;
+}
 
 constexpr int kMaxTp = 8;  // MAX_TP of getp-csrc/nccl.hpp:6
 // Symmetric buffers of a tensor-parallel group as seen from one rank: entry r is rank r's buffer
@@ -85,7 +91,7 @@ struct GemmArgs {
   const __nv_bfloat16 *bias;  // [E][R]
   int add_bias;               // MLP2 on TP ranks other than 0 leaves the bias out
   uint8_t *hq_out;            // MLP1: quantised SwiGLU output [tiles*kTileM, ld_out] e4m3 (high/low rows)
-  float *y_out;               // MLP2: [P, ld_out] fp32
+  __half *y_out;              // MLP2: [P, ld_out] fp16
   int ld_out;
   int h_exp;                  // MLP1: SwiGLU outputs are stored as e4m3(h * 2^-h_exp)
   float limit, alpha;
@@ -144,7 +150,7 @@ struct moe_ctx {
   int *tile_base = nullptr;         // first token tile of each expert [E+1]
   int max_tiles = 0;
   int h_exp = 0;                    // hq holds e4m3(h * 2^-h_exp)
-  float *ybuf = nullptr;            // expert_output_partial [max_pairs, H] fp32
+  __half *ybuf = nullptr;           // expert_output_partial [max_pairs, H] fp16
   float *out_f32 = nullptr;         // fp32 block output   [max_rows, H] (debug / TP partial)
   __nv_bfloat16 *out_bf16 = nullptr;// e_agg_g             [max_rows, H]
   moe::WorkItem *work1 = nullptr, *work2 = nullptr;
@@ -190,7 +196,7 @@ void launch_quantize_rows(const __nv_bfloat16 *t, const int *row_token, const in
 int quantize_rows_max_hidden();
 void launch_gather_rows(const __nv_bfloat16 *t, const int *row_token, const int *offsets, int E, __half *xperm,
                         int H, int max_pairs, cudaStream_t s);
-void launch_combine(const float *y, const int *topk_idx, const float *topk_w, const int *pair_row, int T, int H,
+void launch_combine(const __half *y, const int *topk_idx, const float *topk_w, const int *pair_row, int T, int H,
                     int K, __nv_bfloat16 *out_bf16, float *out_f32, cudaStream_t s, int tp = 0,
                     const TpPeers *peers = nullptr, int rows_local = 0, int rank = 0,
                     const __nv_bfloat16 *residual = nullptr);
@@ -219,7 +225,7 @@ void launch_simt_mlp1(const uint8_t *w_tiles, const uint8_t *scales_raw, const _
                       const __half *x, const int *offsets, int E, int H, int R1, __half *h_out, int ld_h,
                       float limit, float alpha, int n_rows, cudaStream_t s);
 void launch_simt_mlp2(const uint8_t *w_tiles, const uint8_t *scales_raw, const __nv_bfloat16 *bias,
-                      int add_bias, const __half *h, const int *offsets, int E, int Dl, int H, float *y_out,
+                      int add_bias, const __half *h, const int *offsets, int E, int Dl, int H, __half *y_out,
                       int n_rows, cudaStream_t s);
 
 // moe_api.cu: the block itself.  With tp_rows_local > 0 this is a call of a tensor-parallel group: t is the

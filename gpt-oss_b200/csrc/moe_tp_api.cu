@@ -186,7 +186,7 @@ int moe_tp_forward_host(moe_handle c, int layer, const void *t_local_host, int r
   cudaMemcpy(&st, c->status, sizeof(st), cudaMemcpyDeviceToHost);
   if (st) {
     cudaMemset(c->status, 0, sizeof(unsigned));
-    return tp_fail(c, (st & ST_BAD_INDEX) ? MOE_ERR_STATE : MOE_ERR_TIMEOUT, "device status word 0x%x", st);
+    return tp_fail(c, status_error(st), "device status word 0x%x", st);
   }
   return MOE_OK;
 }

@@ -514,7 +514,7 @@ void launch_gather_rows(const __nv_bfloat16 *t, const int *row_token, const int 
 // reduce_tokenwise_expert_outputs_bf16_bf16wts (kernels/moe.hpp:700-730).
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
-combine_kernel(const float *__restrict__ y, const int *__restrict__ topk_idx, const float *__restrict__ topk_w,
+combine_kernel(const __half *__restrict__ y, const int *__restrict__ topk_idx, const float *__restrict__ topk_w,
                const int *__restrict__ pair_row, int T, int H, int K, __nv_bfloat16 *__restrict__ out_bf16,
                float *__restrict__ out_f32, int tp, TpPeers peers, int rows_local, int rank,
                const __nv_bfloat16 *__restrict__ residual) {
@@ -540,7 +540,10 @@ combine_kernel(const float *__restrict__ y, const int *__restrict__ topk_idx, co
   for (int i = threadIdx.x; i < H / 4; i += blockDim.x) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int k = 0; k < K; ++k) {
-      const float4 v = __ldg(reinterpret_cast<const float4 *>(y + static_cast<size_t>(row[k]) * H) + i);
+      const uint2 raw = __ldg(reinterpret_cast<const uint2 *>(y + static_cast<size_t>(row[k]) * H) + i);
+      const float2 v01 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
+      const float2 v23 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
+      const float4 v = make_float4(v01.x, v01.y, v23.x, v23.y);
       acc.x = __fadd_rn(acc.x, __fmul_rn(v.x, wt[k]));
       acc.y = __fadd_rn(acc.y, __fmul_rn(v.y, wt[k]));
       acc.z = __fadd_rn(acc.z, __fmul_rn(v.z, wt[k]));
@@ -564,7 +567,7 @@ combine_kernel(const float *__restrict__ y, const int *__restrict__ topk_idx, co
   }
 }
 
-void launch_combine(const float *y, const int *topk_idx, const float *topk_w, const int *pair_row, int T, int H,
+void launch_combine(const __half *y, const int *topk_idx, const float *topk_w, const int *pair_row, int T, int H,
                     int K, __nv_bfloat16 *out_bf16, float *out_f32, cudaStream_t s, int tp, const TpPeers *peers,
                     int rows_local, int rank, const __nv_bfloat16 *residual) {
   TpPeers pv = {};

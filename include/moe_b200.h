@@ -32,7 +32,8 @@ enum {
   MOE_ERR_TIMEOUT = 4,     /* a bounded device- or host-side wait ran out */
   MOE_ERR_SCALE_RANGE = 5, /* an E8M0 weight scale byte is 0xFF (NaN) */
   MOE_ERR_STATE = 6,       /* layer not loaded, peers not attached, ... */
-  MOE_ERR_NO_SM100 = 7     /* device is not compute capability 10.x */
+  MOE_ERR_NO_SM100 = 7,    /* device is not compute capability 10.x */
+  MOE_ERR_Y_RANGE = 8      /* an MLP2 output exceeded 65504 in magnitude (it is kept in fp16 until the combine) */
 };
 
 /* moe_config.flags */
@@ -205,7 +206,7 @@ enum {
   MOE_DBG_ROW_TOKEN = 6,/* i32 [rows*K]     expert_row_token_g */
   MOE_DBG_OUT_F32 = 7,  /* f32 [rows, H]    block output before the bf16 rounding (MOE_CFG_KEEP_F32_OUT) */
   MOE_DBG_STATUS = 8,   /* u32 [4096]       device status word (first element) and diagnostics */
-  MOE_DBG_YBUF = 10,    /* f32 [rows*K, H]  MLP2 output, permuted rows (expert_output_partial_g) */
+  MOE_DBG_YBUF = 10,    /* f16 [rows*K, H]  MLP2 output, permuted rows (expert_output_partial_g) */
   MOE_DBG_GATHER = 11,  /* bf16 [rows, H]   all-gather destination of the TP group (gather_x_g) */
   MOE_DBG_TNORM = 12    /* bf16 [rows_local, H]  RMS-normalised rows of the last moe_block() (state.t) */
 };

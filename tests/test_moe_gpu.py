@@ -405,3 +405,25 @@ def test_forward_in_a_cuda_graph(pkg, synth):
         blk.synchronize()
     finally:
         blk.close()
+
+
+def test_expert_output_beyond_fp16_is_reported(pkg, synth):
+    """The per-(token, expert) MLP2 outputs wait for the combine in fp16; a magnitude above 65504 is an
+    error code, not a silent infinity, and the handle keeps working."""
+    E, H, D, T = 8, 128, 128, 20
+    layer = synth.make_layer(E, H, D, seed=51)
+    tokens = synth.make_tokens(T, H, seed=52)
+    bad = dict(layer)
+    bad["b2"] = layer["b2"].copy()
+    bad["b2"][:, 5] = synth.f32_to_bf16_bits(np.float32(1.0e5))
+    blk = pkg.MoeBlock(H, D, E, max_rows=T, n_layers=2)
+    try:
+        blk.load_layer(0, layer)
+        blk.load_layer(1, bad)
+        good = blk.forward_host(0, tokens).copy()
+        with pytest.raises(pkg.MoeError) as ei:
+            blk.forward_host(1, tokens)
+        assert ei.value.code == 8
+        assert np.array_equal(blk.forward_host(0, tokens), good)
+    finally:
+        blk.close()
