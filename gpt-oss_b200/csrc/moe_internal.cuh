@@ -66,15 +66,15 @@ struct HostSlot {
   long long ticket = -1;                         // call that owns the slot; -1: free
 };
 
-// One work item of the grouped GEMM: one token tile against one or two adjacent kTileN-row blocks of the
-// expert's weight matrix (two, except for the last block of an odd count).
+// One work item of the grouped GEMM: one token tile against nblk adjacent kTileN-row blocks of the expert's
+// weight matrix, processed one after the other (the index kernel emits single blocks).
 struct __align__(16) WorkItem {
   int expert;  // expert index
   int ntile;   // first kTileN-row block of that expert's weight matrix
   int tile;    // global token-tile index (rows tile*kTileM .. of the quantised activations)
   int row0;    // first permuted row of the token tile
   int ntok;    // valid token rows in the tile (1..kTokTile)
-  int nblk;    // row blocks in this item: 1 or 2
+  int nblk;    // row blocks in this item
   int pad[2];
 };
 

@@ -346,28 +346,30 @@ build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ cou
   }
   if (tid == 0 && s_running != cnt) atomicOr(status, ST_BAD_INDEX);
 
-  // work items: one per (token tile of kTokTile rows, PAIR of kTileN-row weight blocks); items that share a
-  // weight block are adjacent so that block is fetched from HBM once and re-read from L2
+  // work items: one per (token tile of kTokTile rows, block of kTileN weight rows); items that share a
+  // weight block are adjacent so that block is fetched from HBM once and re-read from L2.  Single blocks
+  // rather than pairs: the items of a launch are dealt round-robin to one CTA per SM, and the finer the
+  // items, the smaller the idle share of the last round (930 pair items of MLP2 over 148 SMs lose 10 %,
+  // 1860 single ones 3 %).
   for (int which = 0; which < 2; ++which) {
     const int nn = which ? n_ntiles2 : n_ntiles1;
-    const int np = (nn + 1) / 2;
     WorkItem *work = which ? work2 : work1;
     const int cap = which ? max_work2 : max_work1;
-    const int start = tiles_before * np;
-    for (int i = tid; i < ntt * np; i += blockDim.x) {
-      const int pr = i / ntt, tt = i % ntt;
+    const int start = tiles_before * nn;
+    for (int i = tid; i < ntt * nn; i += blockDim.x) {
+      const int nt = i / ntt, tt = i % ntt;
       WorkItem it;
       it.expert = e;
-      it.ntile = 2 * pr;
+      it.ntile = nt;
       it.tile = tiles_before + tt;
       it.row0 = off + tt * kTokTile;
       it.ntok = min(kTokTile, cnt - tt * kTokTile);
-      it.nblk = min(2, nn - 2 * pr);
+      it.nblk = 1;
       it.pad[0] = it.pad[1] = 0;
       if (start + i < cap) work[start + i] = it;
       else atomicOr(status, ST_BAD_INDEX);
     }
-    if (e == E - 1 && tid == 0) n_work[which] = min((tiles_before + ntt) * np, cap);
+    if (e == E - 1 && tid == 0) n_work[which] = min((tiles_before + ntt) * nn, cap);
   }
 }
 
