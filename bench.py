@@ -12,7 +12,7 @@ data path) and the value is the sum over ranks.
 
 One JSON line is printed by rank 0.  `value` is device-resident throughput
 (CUDA events on the launching stream), `e2e` goes through the host-buffer entry points
-(moe_forward_host_submit/_wait on one GPU, three batches in flight; moe_tp_forward_host in a TP group) with
+(moe_forward_host_submit/_wait, three batches in flight, every rank of a TP group with its own rows) with
 pinned host buffers (every step's copies inside the timed region), `roofline` describes the
 dominant kernel (the MLP1 grouped GEMM) from per-stage CUDA events, and
 `cpu_baseline` times the reference's own CPU forward() on the host cores over a
@@ -276,9 +276,9 @@ def main():
     active = int((counts > 0).sum())
 
     # ---- C: end to end through the host-buffer entry points -----------------
-    # Every step copies its rows in from pinned host memory and its result back out.  One GPU: submit/wait,
-    # up to three batches in flight, so the copies of neighbouring steps overlap the block of this one (what a
-    # serving loop does).  TP group: the blocking call.
+    # Every step copies its rows in from pinned host memory and its result back out: submit/wait, up to three
+    # batches in flight, so the copies of neighbouring steps overlap the block of this one (what a serving
+    # loop does).  In a TP group every rank submits its own rows, in the same order.
     n_pin = 3
     pin_in = [pkg.PinnedBuffer((T, H), np.uint16) for _ in range(n_pin)]
     pin_out = [pkg.PinnedBuffer((T, H), np.uint16) for _ in range(n_pin)]
@@ -286,10 +286,6 @@ def main():
         b.array[:] = tokens
 
     def host_steps(n):
-        if tp > 1:
-            for i in range(n):
-                blk.tp_forward_host(0, pin_in[i % n_pin].array, pin_out[i % n_pin].array)
-            return
         tickets = []
         for i in range(n):
             if len(tickets) == n_pin:
@@ -363,8 +359,7 @@ def main():
         "config": cfg,
         "e2e": {"value": world * T * args.steps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": T * H * 2,
                 "d2h_bytes_per_step": T * H * 2, "ms_per_step": e2e_s / args.steps * 1e3,
-                "api": "moe_tp_forward_host (blocking)" if tp > 1 else
-                       "moe_forward_host_submit/_wait, 3 batches in flight, pinned buffers"},
+                "api": "moe_forward_host_submit/_wait, 3 batches in flight, pinned buffers"},
         "gpu_launches": gpu_launches,
         "clocks": clocks,
         "roofline": {"kernel": "expert_gemm_kernel<1> (MLP1 grouped GEMM + SwiGLU)", "bound": "hbm",

@@ -204,7 +204,7 @@ class MoeBlock:
         ticket = C.c_longlong(-1)
         self._check(self.L.moe_forward_host_submit(self.h, layer, t_bits.ctypes.data_as(C.c_void_p), t_bits.shape[0],
                                                    out.ctypes.data_as(C.c_void_p), flags, C.byref(ticket)))
-        self.rows = t_bits.shape[0]
+        self.rows = t_bits.shape[0] * self.cfg.tp_size
         return ticket.value
 
     def forward_host_wait(self, ticket: int):

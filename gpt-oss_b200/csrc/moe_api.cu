@@ -585,12 +585,11 @@ int host_slot_finish(moe_ctx *c, HostSlot &hs) {
 int moe_forward_host_submit(moe_handle c, int layer, const void *t_host, int rows, void *out_host, unsigned flags,
                             long long *ticket) {
   if (!c) return MOE_ERR_INVALID;
-  if (!t_host || !out_host || !ticket || rows <= 0 || rows > c->max_rows)
-    return fail(c, MOE_ERR_INVALID, "moe_forward_host_submit: bad arguments");
-  if (c->cfg.tp_size > 1) return fail(c, MOE_ERR_STATE, "moe_forward_host_submit: single-GPU handles only");
-  CU_TRY(c, cudaSetDevice(c->cfg.device));
-  int rc = host_pipeline_init(c);
+  if (!t_host || !out_host || !ticket) return fail(c, MOE_ERR_INVALID, "moe_forward_host_submit: bad arguments");
+  const int tp = c->cfg.tp_size;
+  int rc = check_tp_call(c, rows, "moe_forward_host_submit");  // rows are this rank's rows
   if (rc != MOE_OK) return rc;
+  if ((rc = host_pipeline_init(c)) != MOE_OK) return rc;
   HostSlot &hs = c->host_slots[c->host_submitted % kHostSlots];
   if (hs.ticket >= 0)
     return fail(c, MOE_ERR_STATE, "moe_forward_host_submit: %d calls in flight, wait for ticket %lld first", kHostSlots,
@@ -601,7 +600,11 @@ int moe_forward_host_submit(moe_handle c, int layer, const void *t_host, int row
   CU_TRY(c, cudaMemcpyAsync(hs.in, t_host, bytes, cudaMemcpyHostToDevice, c->h2d_stream));
   CU_TRY(c, cudaEventRecord(hs.in_ready, c->h2d_stream));
   CU_TRY(c, cudaStreamWaitEvent(c->stream, hs.in_ready, 0));
-  rc = forward_impl(c, layer, hs.in, rows, hs.out, flags & ~MOE_FWD_PARTIAL_F32, c->stream, nullptr, 0);
+  if (tp > 1)
+    rc = forward_impl(c, layer, static_cast<const __nv_bfloat16 *>(c->peers.gather[c->cfg.tp_rank]), rows * tp, hs.out,
+                      flags & ~MOE_FWD_PARTIAL_F32, c->stream, hs.in, rows);
+  else
+    rc = forward_impl(c, layer, hs.in, rows, hs.out, flags & ~MOE_FWD_PARTIAL_F32, c->stream, nullptr, 0);
   if (rc != MOE_OK) return rc;
   CU_TRY(c, cudaEventRecord(hs.out_ready, c->stream));
   CU_TRY(c, cudaStreamWaitEvent(c->d2h_stream, hs.out_ready, 0));

@@ -228,6 +228,9 @@ void launch_simt_mlp2(const uint8_t *w_tiles, const uint8_t *scales_raw, const _
                       int add_bias, const __half *h, const int *offsets, int E, int Dl, int H, __half *y_out,
                       int n_rows, cudaStream_t s);
 
+// moe_tp_api.cu: argument and group checks shared by the calls of a tensor-parallel group.
+int check_tp_call(moe_ctx *c, int rows_local, const char *who);
+
 // moe_api.cu: the block itself.  With tp_rows_local > 0 this is a call of a tensor-parallel group: t is the
 // gather buffer, t_local this rank's rows; routing is computed for the local rows only and exchanged, the
 // combine pushes each row's partial to the rank that owns it, and out_dev receives this rank's summed rows.

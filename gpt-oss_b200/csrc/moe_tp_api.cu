@@ -39,6 +39,9 @@ bool group_complete(const moe_ctx *c) {
   return true;
 }
 
+}  // namespace
+
+namespace moe {
 int check_tp_call(moe_ctx *c, int rows_local, const char *who) {
   if (c->cfg.tp_size > 1 && !group_complete(c))
     return tp_fail(c, MOE_ERR_STATE, "%s: not every peer buffer of the %d-rank group is attached", who, c->cfg.tp_size);
@@ -48,8 +51,7 @@ int check_tp_call(moe_ctx *c, int rows_local, const char *who) {
   if (cudaSetDevice(c->cfg.device) != cudaSuccess) return tp_fail(c, MOE_ERR_CUDA, "%s: cudaSetDevice failed", who);
   return MOE_OK;
 }
-
-}  // namespace
+}  // namespace moe
 
 extern "C" {
 

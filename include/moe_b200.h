@@ -129,6 +129,8 @@ int moe_forward_host(moe_handle h, int layer, const void *t_host, int rows, void
  * returns at once with a ticket; wait blocks until that batch's result is in out_host.  Up to three
  * batches may be in flight (a fourth submit fails with MOE_ERR_STATE until the oldest was waited for);
  * both host buffers must stay valid, and should be pinned (moe_host_alloc), until the wait returns.
+ * With tp_size > 1 the rows are this rank's rows and every rank of the group submits its batches in
+ * the same order (the call is then moe_tp_forward_host split in two).
  * The reference has no counterpart: its forward_batch_gpu (getp_run.cpp:3254) copies tokens in, runs
  * and copies logits out on one stream, blocking the host thread. */
 int moe_forward_host_submit(moe_handle h, int layer, const void *t_host, int rows, void *out_host,

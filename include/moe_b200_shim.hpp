@@ -91,6 +91,17 @@ inline void moe_gpu_b200(const TPGroup &tp, int layer_idx, const void *t_rows, i
   if (rc != MOE_OK) moe_b200_die(h, "moe_gpu_b200", rc);
 }
 
+// moe_gpu / moe_gpu_120b as a whole, steps 0-10: `x_rows` are this device's rows of the residual stream
+// (state.x + row_offset*H), normalised with `rms_ffn_w` (the layer's gain, bf16 [H]), run through the block
+// and the group's exchange, and updated in place.
+inline void moe_gpu_b200_block(const TPGroup &tp, int layer_idx, void *x_rows, const void *rms_ffn_w, int batch_size,
+                               cudaStream_t sMoe) {
+  if (batch_size <= 0) return;
+  moe_handle h = moe_b200_handles()[tp.world_rank];
+  const int rc = moe_block(h, layer_idx, x_rows, rms_ffn_w, batch_size, 0, sMoe);
+  if (rc != MOE_OK) moe_b200_die(h, "moe_gpu_b200_block", rc);
+}
+
 // ring_allgather_rows_bf16 (getp-csrc/tp_ring.hpp:70-118): the gathered [TP*R_local, C] rows end up in
 // the handle's gather buffer (moe_tp_buffer(h, MOE_TP_BUF_GATHER)); C must be the hidden size.
 inline void ring_allgather_rows_bf16(const void *my_src, int R_local, const TPGroup &tp, cudaStream_t s) {

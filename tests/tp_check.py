@@ -72,6 +72,22 @@ def main():
     b_rms = max(1.0, float(np.sqrt((b_agg.astype(np.float64) ** 2).mean())))
     bound = (2e-2 * b_rms + 2.0 ** -8 * np.abs(b_xo[sl]))[ok_rows]
     assert (b_err <= bound).all(), float((b_err - bound).max())
+    # host buffers, three batches in flight on every rank: the bits of the blocking call
+    batches = [pkg.synth.make_tokens(rows_local * world, H, seed=20 + i)[sl] for i in range(5)]
+    want = [blk.tp_forward_host(0, np.ascontiguousarray(b), np.empty_like(b)).copy() for b in batches]
+    pin_i = [pkg.PinnedBuffer(b.shape, np.uint16) for b in batches]
+    pin_o = [pkg.PinnedBuffer(b.shape, np.uint16) for b in batches]
+    for p_, b in zip(pin_i, batches):
+        p_.array[:] = b
+    tickets = []
+    for i in range(len(batches)):
+        if len(tickets) == 3:
+            blk.forward_host_wait(tickets.pop(0))
+        tickets.append(blk.forward_host_submit(0, pin_i[i].array, pin_o[i].array))
+    for t in tickets:
+        blk.forward_host_wait(t)
+    for i, w_ in enumerate(want):
+        assert np.array_equal(pin_o[i].array, w_), f"pipelined batch {i} differs from the blocking call"
     dist.barrier()
     print(f"rank {rank}: tp_forward ok, mean rel {mean_rel:.2e}, max abs {err.max():.3e} (rms {rms:.2f})", flush=True)
     blk.close()
