@@ -241,11 +241,6 @@ def main():
         else:
             blk.forward(0, d_t.data_ptr(), T, d_o.data_ptr(), 0, sp)
 
-    # The GPU sat idle while the host built the synthetic layer (seconds): a quarter of a second of untimed
-    # steps first, so that the W warm-up steps and the timed ones see settled clocks rather than the ramp.
-    for _ in range(max(1, int(0.25 / 0.6e-3))):
-        step()
-    torch.cuda.synchronize()
     for _ in range(warmup):
         step()
     torch.cuda.synchronize()
