@@ -146,7 +146,7 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
           if (!mbar_wait(empty_bar(s), ((it / kStages) & 1u) ^ 1u, abort_flag, p.status, ST_WAIT_EMPTY)) { ok = false; break; }
           const uint32_t stage = smem_base + s * kStageBytes;
           mbar_arrive_expect_tx(full_bar(s), kABytes + kWLoadBytes + kSfbChunkBytes);
-          tma_load_2d(stage, &tm_x, kc * kChunkK, w.tile * kTileM, full_bar(s));
+          tma_load_2d(stage, &tm_x, 0, (w.tile * nkc + kc) * kTileM, full_bar(s));   // one contiguous 16 KB tile
           // weights pass through once per step: they must not push the activations and the results out of L2
           tma_load_3d_hint(stage + kABytes, &tm_w, 0, 0, static_cast<int>(tile0 + kc), full_bar(s), w_policy);
           bulk_load_hint(stage + kABytes + kWBytes, p.w_tiles + static_cast<size_t>(tile0 + kc) * kWTileStride + kWTileCodes,
@@ -273,11 +273,12 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 #pragma unroll
           for (int i = 0; i < 4; ++i) r[i] = (hs[i] - e4m3_to_float((hi4 >> (8 * i)) & 0xffu)) * 16.0f;
           const uint32_t lo4 = pack_e4m3x4(r[0], r[1], r[2], r[3]);
-          const int j = nc >> 1;  // this lane's 4 intermediate features j .. j+3
+          const int j = p.hq_joff + (nc >> 1);  // this lane's 4 intermediate features, as columns of MLP2's k window
           if (tok_ok && nc < p.R) {
-            uint8_t *dst = p.hq_out + (static_cast<size_t>(w.tile) * kTileM + 2 * tok) * p.ld_out + j;
+            // MLP2's activation tiles: [tile][k slice][128 rows][128 bytes]
+            uint8_t *dst = p.hq_out + ((static_cast<size_t>(w.tile) * p.hq_nkc + (j >> 7)) * kTileM + 2 * tok) * kChunkK + (j & 127);
             *reinterpret_cast<uint32_t *>(dst) = hi4;
-            *reinterpret_cast<uint32_t *>(dst + p.ld_out) = lo4;
+            *reinterpret_cast<uint32_t *>(dst + kChunkK) = lo4;
           }
         } else {
           const int na = n0 + c0 + 8 * odd;  // first of this lane's 8 columns

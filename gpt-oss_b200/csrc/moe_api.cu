@@ -71,18 +71,22 @@ int make_weight_map(moe_ctx *c, CUtensorMap *m, const uint8_t *base, size_t n_ti
   return MOE_OK;
 }
 
-// e4m3 activation rows [rows][K] (one byte each), box = 128 elements x 128 rows, 128-byte swizzle.
-int make_act_map(moe_ctx *c, CUtensorMap *m, const uint8_t *base, int rows, int K) {
+// e4m3 activation tiles: [token tile][k slice][128 rows][128 bytes], so that the 16 KB a work item needs for one
+// k slice are one contiguous run (rows of K bytes would make the box 128 separate 128-byte pieces).  To TMA
+// this is a matrix of 128-byte rows; box = 128 x 128, 128-byte swizzle.
+int make_act_map(moe_ctx *c, CUtensorMap *m, const uint8_t *base, size_t n_tiles, int n_kc) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(c, MOE_ERR_CUDA, "cuTensorMapEncodeTiled not available");
-  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K)};
+  const cuuint64_t rows = static_cast<cuuint64_t>(n_tiles) * n_kc * kTileM;
+  const cuuint64_t dims[2] = {kChunkK, rows};
+  const cuuint64_t strides[1] = {kChunkK};
   const cuuint32_t box[2] = {kChunkK, kTileM};
   const cuuint32_t es[2] = {1, 1};
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(base), dims, strides, box, es,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(c, MOE_ERR_CUDA, "cuTensorMapEncodeTiled(activations rows=%d K=%d) -> %d", rows, K, (int)r);
+  if (r != CUDA_SUCCESS)
+    return fail(c, MOE_ERR_CUDA, "cuTensorMapEncodeTiled(activations, %zu tiles x %d slices) -> %d", n_tiles, n_kc, (int)r);
   return MOE_OK;
 }
 
@@ -211,7 +215,8 @@ int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_b
     a.work = c->work1; a.n_work = c->n_work; a.K = H; a.R = c->R1;
     a.n_kchunks = (H + kChunkK - 1) / kChunkK; a.n_ntiles = n_nt1;
     a.w_tiles = w.w1_tiles; a.sfa = c->sfa_x; a.sfa_tile_stride = kSfAtomBytes; a.bias = w.b1; a.add_bias = 1;
-    a.hq_out = c->hq + c->joff; a.y_out = nullptr; a.ld_out = c->Kw; a.h_exp = c->h_exp;
+    a.hq_out = c->hq; a.hq_joff = c->joff; a.hq_nkc = (c->Kw + kChunkK - 1) / kChunkK; a.y_out = nullptr; a.ld_out = c->Kw;
+    a.h_exp = c->h_exp;
     a.limit = c->cfg.swiglu_limit; a.alpha = c->cfg.swiglu_alpha; a.status = c->status;
     launch_expert_gemm_mlp1(w.tm_w1, c->tm_x1, a, c->sm_count, s);
     mark();
@@ -362,14 +367,17 @@ int moe_create(const moe_config *cfg, moe_handle *out) {
     const float bound = fmaxf(c->cfg.swiglu_limit * (c->cfg.swiglu_limit + 1.0f), 1.0f);
     c->h_exp = static_cast<int>(ceilf(log2f(bound))) - 8;
   }
-  const size_t tile_rows = static_cast<size_t>(c->max_tiles) * kTileM;
-  if ((rc = dev_alloc(c, &c->xq, tile_rows * c->H))) return rc;
-  if ((rc = dev_alloc(c, &c->hq, tile_rows * c->Kw))) return rc;
+  const int n_kc1 = (c->H + kChunkK - 1) / kChunkK, n_kc2 = (c->Kw + kChunkK - 1) / kChunkK;
+  const size_t act_tile = static_cast<size_t>(kTileM) * kChunkK;   // 16 KB per (token tile, k slice)
+  const size_t xq_bytes = static_cast<size_t>(c->max_tiles) * n_kc1 * act_tile;
+  const size_t hq_bytes = static_cast<size_t>(c->max_tiles) * n_kc2 * act_tile;
+  if ((rc = dev_alloc(c, &c->xq, xq_bytes))) return rc;
+  if ((rc = dev_alloc(c, &c->hq, hq_bytes))) return rc;
   if ((rc = dev_alloc(c, &c->sfa_x, static_cast<size_t>(c->max_tiles) * kSfAtomBytes))) return rc;
   if ((rc = dev_alloc(c, &c->sfa_h, static_cast<size_t>(kSfAtomBytes)))) return rc;
   if ((rc = dev_alloc(c, &c->tile_base, static_cast<size_t>(c->E) + 1))) return rc;
-  CU_TRY(c, cudaMemset(c->xq, 0, tile_rows * c->H));
-  CU_TRY(c, cudaMemset(c->hq, 0, tile_rows * c->Kw));
+  CU_TRY(c, cudaMemset(c->xq, 0, xq_bytes));   // bytes past K in the last slice and never-written columns stay 0
+  CU_TRY(c, cudaMemset(c->hq, 0, hq_bytes));
   CU_TRY(c, cudaMemset(c->sfa_x, 127, static_cast<size_t>(c->max_tiles) * kSfAtomBytes));
   {
     uint8_t atom[kSfAtomBytes];
@@ -387,8 +395,8 @@ int moe_create(const moe_config *cfg, moe_handle *out) {
   // Rows past the current batch are read (and discarded) by token tiles that overhang; keep them finite.
   CU_TRY(c, cudaMemset(c->xperm, 0, P * c->H * sizeof(__half)));
   CU_TRY(c, cudaMemset(c->hbuf, 0, P * c->Kw * sizeof(__half)));
-  if ((rc = make_act_map(c, &c->tm_x1, c->xq, static_cast<int>(tile_rows), c->H))) return rc;
-  if ((rc = make_act_map(c, &c->tm_x2, c->hq, static_cast<int>(tile_rows), c->Kw))) return rc;
+  if ((rc = make_act_map(c, &c->tm_x1, c->xq, c->max_tiles, n_kc1))) return rc;
+  if ((rc = make_act_map(c, &c->tm_x2, c->hq, c->max_tiles, n_kc2))) return rc;
   return MOE_OK;
 }
 

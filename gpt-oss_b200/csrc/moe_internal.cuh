@@ -90,7 +90,8 @@ struct GemmArgs {
   int sfa_tile_stride;        // bytes between token tiles' atoms (0: one atom shared by all tiles)
   const __nv_bfloat16 *bias;  // [E][R]
   int add_bias;               // MLP2 on TP ranks other than 0 leaves the bias out
-  uint8_t *hq_out;            // MLP1: quantised SwiGLU output [tiles*kTileM, ld_out] e4m3 (high/low rows)
+  uint8_t *hq_out;            // MLP1: quantised SwiGLU output, e4m3 tiles [tile][hq_nkc][128 rows][128 bytes]
+  int hq_joff, hq_nkc;        //       column of the shard's first output inside MLP2's k window; its k slices
   __half *y_out;              // MLP2: [P, ld_out] fp16
   int ld_out;
   int h_exp;                  // MLP1: SwiGLU outputs are stored as e4m3(h * 2^-h_exp)
@@ -143,8 +144,8 @@ struct moe_ctx {
   int *row_slot = nullptr;          // row of the token's high term in xq [max_pairs]
   __half *xperm = nullptr;          // expert_input_buffer [max_pairs, H]   fp16 (validation GEMM only)
   __half *hbuf = nullptr;           // gate_up             [max_pairs, Dl]  fp16 (validation GEMM only)
-  uint8_t *xq = nullptr;            // expert_input_buffer as e4m3 high/low rows [max_tiles*128, H]
-  uint8_t *hq = nullptr;            // gate_up as e4m3 high/low rows            [max_tiles*128, Dl]
+  uint8_t *xq = nullptr;            // expert_input_buffer as e4m3 high/low rows, [max_tiles][k slices][128 rows][128 B]
+  uint8_t *hq = nullptr;            // gate_up as e4m3 high/low rows, same tiling over MLP2's k window
   uint8_t *sfa_x = nullptr;         // per-tile scale atoms of xq [max_tiles][512]
   uint8_t *sfa_h = nullptr;         // the one scale atom of hq   [512]
   int *tile_base = nullptr;         // first token tile of each expert [E+1]
