@@ -146,11 +146,12 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
           if (!mbar_wait(empty_bar(s), ((it / kStages) & 1u) ^ 1u, abort_flag, p.status, ST_WAIT_EMPTY)) { ok = false; break; }
           const uint32_t stage = smem_base + s * kStageBytes;
           mbar_arrive_expect_tx(full_bar(s), kABytes + kWLoadBytes + kSfbChunkBytes);
-          tma_load_2d(stage, &tm_x, 0, (w.tile * nkc + kc) * kTileM, full_bar(s));   // one contiguous 16 KB tile
-          // weights pass through once per step: they must not push the activations and the results out of L2
+          // the weight tile first: it has the longer way (HBM; the activations come from L2).  Weights pass
+          // through once per step: they must not push the activations and the results out of L2
           tma_load_3d_hint(stage + kABytes, &tm_w, 0, 0, static_cast<int>(tile0 + kc), full_bar(s), w_policy);
           bulk_load_hint(stage + kABytes + kWBytes, p.w_tiles + static_cast<size_t>(tile0 + kc) * kWTileStride + kWTileCodes,
                          kSfbChunkBytes, full_bar(s), w_policy);
+          tma_load_2d(stage, &tm_x, 0, (w.tile * nkc + kc) * kTileM, full_bar(s));   // one contiguous 16 KB tile
         }
        }
       }
