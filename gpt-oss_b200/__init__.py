@@ -27,7 +27,7 @@ FWD_SIMT_GEMM = 1
 FWD_PARTIAL_F32 = 2
 
 DBG_LOGITS, DBG_TOPK_IDX, DBG_TOPK_W, DBG_COUNTS, DBG_OFFSETS, DBG_PAIR_ROW, DBG_ROW_TOKEN, DBG_OUT_F32, \
-    DBG_STATUS, DBG_HBUF, DBG_YBUF, DBG_GATHER, DBG_TNORM = range(13)
+    DBG_STATUS, DBG_HBUF, DBG_YBUF, DBG_GATHER, DBG_TNORM, DBG_TP_PARTIAL = range(14)
 
 EXPORTS = [
     "moe_create", "moe_destroy", "moe_load_layer", "moe_shard_range", "moe_forward", "moe_forward_host",
@@ -282,7 +282,8 @@ class MoeBlock:
             DBG_COUNTS: ((E,), np.int32), DBG_OFFSETS: ((E + 1,), np.int32), DBG_PAIR_ROW: ((T, K), np.int32),
             DBG_ROW_TOKEN: ((T * K,), np.int32), DBG_OUT_F32: ((T, H), np.float32),
             DBG_STATUS: ((1,), np.uint32), DBG_YBUF: ((T * K, H), np.float16),
-            DBG_GATHER: ((T, H), np.uint16), DBG_TNORM: ((T // self.cfg.tp_size, H), np.uint16)}[which]
+            DBG_GATHER: ((T, H), np.uint16), DBG_TNORM: ((T // self.cfg.tp_size, H), np.uint16),
+            DBG_TP_PARTIAL: ((T, H), np.uint16)}[which]
         out = np.empty(shape, dtype=dt)
         self._check(self.L.moe_get_debug(self.h, which, out.ctypes.data_as(C.c_void_p), out.nbytes))
         return out

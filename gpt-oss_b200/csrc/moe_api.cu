@@ -151,7 +151,9 @@ void free_layer(LayerWeights &w) {
 namespace moe {
 
 int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_bfloat16 *out_dev, unsigned flags,
-                 cudaStream_t s, const __nv_bfloat16 *t_local, int tp_rows_local, const __nv_bfloat16 *residual) {
+                 cudaStream_t s, const __nv_bfloat16 *t_local, int tp_rows_local, const __nv_bfloat16 *residual,
+                 unsigned int *status) {
+  if (status == nullptr) status = c->status;
   if (layer < 0 || layer >= c->L || !t || rows <= 0 || rows > c->max_rows)
     return fail(c, MOE_ERR_INVALID, "moe_forward: layer %d rows %d (max %d)", layer, rows, c->max_rows);
   if (!out_dev && !(flags & MOE_FWD_PARTIAL_F32)) return fail(c, MOE_ERR_INVALID, "moe_forward: null output");
@@ -192,13 +194,13 @@ int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_b
     launch_topk_softmax(c->logits, c->router_part, splits, w.router_b, tp_rows_local, E, K, nullptr, nullptr, nullptr, s,
                         tp, &c->peers, rank * tp_rows_local);
     CU_TRY(c, cudaStreamWaitEvent(s, c->ev_join, 0));
-    launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, 0, c->tp_epoch, c->status, s);
+    launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, 0, c->tp_epoch, status, s);
     launch_count_experts(c->topk_idx, T * K, E, c->counts, s);
     mark();
     c->launches += 3;
   }
   launch_build_index(c->topk_idx, c->counts, T, E, K, n_nt1, n_nt2, c->offsets, c->tile_base, c->pair_row,
-                     c->row_token, c->row_slot, c->work1, c->work2, c->n_work, c->max_work1, c->max_work2, c->status, s);
+                     c->row_token, c->row_slot, c->work1, c->work2, c->n_work, c->max_work1, c->max_work2, status, s);
   mark();
   if (flags & MOE_FWD_SIMT_GEMM) launch_gather_rows(t, c->row_token, c->offsets, E, c->xperm, H, P, s);
   else launch_quantize_rows(t, c->row_token, c->row_slot, c->offsets + E, c->xq, c->sfa_x, H, P, s);
@@ -217,7 +219,7 @@ int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_b
     a.w_tiles = w.w1_tiles; a.sfa = c->sfa_x; a.sfa_tile_stride = kSfAtomBytes; a.bias = w.b1; a.add_bias = 1;
     a.hq_out = c->hq; a.hq_joff = c->joff; a.hq_nkc = (c->Kw + kChunkK - 1) / kChunkK; a.y_out = nullptr; a.ld_out = c->Kw;
     a.h_exp = c->h_exp;
-    a.limit = c->cfg.swiglu_limit; a.alpha = c->cfg.swiglu_alpha; a.status = c->status;
+    a.limit = c->cfg.swiglu_limit; a.alpha = c->cfg.swiglu_alpha; a.status = status;
     launch_expert_gemm_mlp1(w.tm_w1, c->tm_x1, a, c->sm_count, s);
     mark();
     GemmArgs b = a;
@@ -239,7 +241,7 @@ int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_b
     launch_combine(c->ybuf, c->topk_idx, c->topk_w, c->pair_row, T, H, K, c->tp_partial,
                    (c->cfg.flags & MOE_CFG_KEEP_F32_OUT) ? c->out_f32 : nullptr, s, tp, &c->peers, tp_rows_local, rank);
     ++c->tp_epoch_rs;
-    launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, 1, c->tp_epoch_rs, c->status, s);
+    launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, 1, c->tp_epoch_rs, status, s);
     launch_tp_sum_slots(c->tp_partial, tp, tp_rows_local, H, out_dev, c->sm_count, s, residual);
     mark();
     c->launches += 2;
@@ -323,6 +325,7 @@ int moe_create(const moe_config *cfg, moe_handle *out) {
   c->sm_count = prop.multiProcessorCount;
   CU_TRY(c, cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
   CU_TRY(c, expert_gemm_init());
+  CU_TRY(c, route_init());
 
   const size_t T = c->max_rows, P = c->max_pairs;
   int rc;
@@ -409,7 +412,7 @@ int moe_destroy(moe_handle c) {
   for (cudaStream_t st : {c->h2d_stream, c->d2h_stream})
     if (st) { cudaStreamSynchronize(st); cudaStreamDestroy(st); }
   for (HostSlot &hs : c->host_slots) {
-    cudaFree(hs.in); cudaFree(hs.out);
+    cudaFree(hs.in); cudaFree(hs.out); cudaFree(hs.status_dev);
     if (hs.status_host) cudaFreeHost(hs.status_host);
     for (cudaEvent_t e : {hs.in_ready, hs.out_ready, hs.done})
       if (e) cudaEventDestroy(e);
@@ -569,6 +572,8 @@ int host_pipeline_init(moe_ctx *c) {
     int rc;
     if ((rc = dev_alloc(c, &hs.in, n))) return rc;
     if ((rc = dev_alloc(c, &hs.out, n))) return rc;
+    if ((rc = dev_alloc(c, &hs.status_dev, static_cast<size_t>(1)))) return rc;
+    CU_TRY(c, cudaMemset(hs.status_dev, 0, sizeof(unsigned)));
     CU_TRY(c, cudaHostAlloc(reinterpret_cast<void **>(&hs.status_host), sizeof(unsigned), cudaHostAllocDefault));
     CU_TRY(c, cudaEventCreateWithFlags(&hs.in_ready, cudaEventDisableTiming));
     CU_TRY(c, cudaEventCreateWithFlags(&hs.out_ready, cudaEventDisableTiming));
@@ -580,11 +585,9 @@ int host_pipeline_init(moe_ctx *c) {
 int host_slot_finish(moe_ctx *c, HostSlot &hs) {
   CU_TRY(c, cudaEventSynchronize(hs.done));
   hs.ticket = -1;
+  // the slot's own status word: what the kernels of THIS call recorded, whatever runs before or after it
   const unsigned st = *hs.status_host;
-  if (st) {
-    CU_TRY(c, cudaMemset(c->status, 0, sizeof(unsigned)));
-    return fail(c, status_error(st), "device status word 0x%x", st);
-  }
+  if (st) return fail(c, status_error(st), "device status word 0x%x", st);
   return MOE_OK;
 }
 
@@ -608,16 +611,18 @@ int moe_forward_host_submit(moe_handle c, int layer, const void *t_host, int row
   CU_TRY(c, cudaMemcpyAsync(hs.in, t_host, bytes, cudaMemcpyHostToDevice, c->h2d_stream));
   CU_TRY(c, cudaEventRecord(hs.in_ready, c->h2d_stream));
   CU_TRY(c, cudaStreamWaitEvent(c->stream, hs.in_ready, 0));
+  CU_TRY(c, cudaMemsetAsync(hs.status_dev, 0, sizeof(unsigned), c->stream));   // cleared in stream order, before the block
   if (tp > 1)
     rc = forward_impl(c, layer, static_cast<const __nv_bfloat16 *>(c->peers.gather[c->cfg.tp_rank]), rows * tp, hs.out,
-                      flags & ~MOE_FWD_PARTIAL_F32, c->stream, hs.in, rows);
+                      flags & ~MOE_FWD_PARTIAL_F32, c->stream, hs.in, rows, nullptr, hs.status_dev);
   else
-    rc = forward_impl(c, layer, hs.in, rows, hs.out, flags & ~MOE_FWD_PARTIAL_F32, c->stream, nullptr, 0);
+    rc = forward_impl(c, layer, hs.in, rows, hs.out, flags & ~MOE_FWD_PARTIAL_F32, c->stream, nullptr, 0, nullptr,
+                      hs.status_dev);
   if (rc != MOE_OK) return rc;
   CU_TRY(c, cudaEventRecord(hs.out_ready, c->stream));
   CU_TRY(c, cudaStreamWaitEvent(c->d2h_stream, hs.out_ready, 0));
   CU_TRY(c, cudaMemcpyAsync(out_host, hs.out, bytes, cudaMemcpyDeviceToHost, c->d2h_stream));
-  CU_TRY(c, cudaMemcpyAsync(hs.status_host, c->status, sizeof(unsigned), cudaMemcpyDeviceToHost, c->d2h_stream));
+  CU_TRY(c, cudaMemcpyAsync(hs.status_host, hs.status_dev, sizeof(unsigned), cudaMemcpyDeviceToHost, c->d2h_stream));
   CU_TRY(c, cudaEventRecord(hs.done, c->d2h_stream));
   hs.ticket = c->host_submitted;
   *ticket = c->host_submitted++;
@@ -687,6 +692,7 @@ int moe_get_debug(moe_handle c, int which, void *dst, size_t bytes) {
     case MOE_DBG_GATHER: src = c->t_in; have = static_cast<size_t>(c->max_rows) * c->H * 2; break;
     case MOE_DBG_TNORM: src = c->t_norm; have = static_cast<size_t>(c->max_rows) * c->H * 2; break;
     case MOE_DBG_YBUF: src = c->ybuf; have = T * c->K * c->H * 2; break;
+    case MOE_DBG_TP_PARTIAL: src = c->tp_partial; have = static_cast<size_t>(c->max_rows) * c->H * 2; break;
     default: return fail(c, MOE_ERR_INVALID, "moe_get_debug: unknown item %d", which);
   }
   if (bytes > have) return fail(c, MOE_ERR_INVALID, "moe_get_debug: %zu bytes asked, %zu available", bytes, have);

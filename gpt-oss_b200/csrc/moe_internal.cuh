@@ -61,7 +61,8 @@ constexpr int kTpBufs = 5;
 constexpr int kHostSlots = 3;
 struct HostSlot {
   __nv_bfloat16 *in = nullptr, *out = nullptr;   // [max_rows, H] each
-  unsigned int *status_host = nullptr;           // pinned copy of the device status word, taken after the block
+  unsigned int *status_dev = nullptr;            // status word of the call that owns the slot (cleared in stream order)
+  unsigned int *status_host = nullptr;           // pinned copy of it, taken after the block
   cudaEvent_t in_ready = nullptr, out_ready = nullptr, done = nullptr;
   long long ticket = -1;                         // call that owns the slot; -1: free
 };
@@ -181,6 +182,7 @@ struct moe_ctx {
 namespace moe {
 
 // route.cu
+cudaError_t route_init();   // per-device kernel attributes; call with the device current
 int router_splits(int T, int H, int sm_count);
 void launch_router_partials(const __nv_bfloat16 *t, const __nv_bfloat16 *w3, float *partial, int T, int H, int E,
                             int splits, cudaStream_t s);
@@ -237,6 +239,6 @@ int check_tp_call(moe_ctx *c, int rows_local, const char *who);
 // combine pushes each row's partial to the rank that owns it, and out_dev receives this rank's summed rows.
 int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int T, __nv_bfloat16 *out_dev, unsigned flags,
                  cudaStream_t s, const __nv_bfloat16 *t_local, int tp_rows_local,
-                 const __nv_bfloat16 *residual = nullptr);
+                 const __nv_bfloat16 *residual = nullptr, unsigned int *status = nullptr);
 
 }  // namespace moe

@@ -136,13 +136,16 @@ int router_splits(int T, int H, int sm_count) {
   return (n_chunks + cps - 1) / cps;  // every split gets at least one chunk
 }
 
+// The router stages more shared memory than a kernel gets by default.  The limit is a property of the
+// (kernel, device) pair, so every device a handle is created on sets it for itself (moe_create calls this
+// with that device current); a flag shared by the whole process would leave the launch rejected on every
+// GPU but the first one a one-process, one-thread-per-GPU caller touches.
+cudaError_t route_init() {
+  return cudaFuncSetAttribute(router_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRtSmem);
+}
+
 void launch_router_partials(const __nv_bfloat16 *t, const __nv_bfloat16 *w3, float *partial, int T, int H, int E,
                             int splits, cudaStream_t s) {
-  static bool attr = false;
-  if (!attr) {
-    cudaFuncSetAttribute(router_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRtSmem);
-    attr = true;
-  }
   const int n_chunks = (H + kRtK - 1) / kRtK, cps = (n_chunks + splits - 1) / splits;
   dim3 grid((T + kRtTok - 1) / kRtTok, splits, (E + kRtExp - 1) / kRtExp);
   router_partial_kernel<<<grid, kRtThreads, kRtSmem, s>>>(t, w3, partial, T, H, E, cps);

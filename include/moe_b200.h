@@ -210,7 +210,8 @@ enum {
   MOE_DBG_STATUS = 8,   /* u32 [4096]       device status word (first element) and diagnostics */
   MOE_DBG_YBUF = 10,    /* f16 [rows*K, H]  MLP2 output, permuted rows (expert_output_partial_g) */
   MOE_DBG_GATHER = 11,  /* bf16 [rows, H]   all-gather destination of the TP group (gather_x_g) */
-  MOE_DBG_TNORM = 12    /* bf16 [rows_local, H]  RMS-normalised rows of the last moe_block() (state.t) */
+  MOE_DBG_TNORM = 12,   /* bf16 [rows_local, H]  RMS-normalised rows of the last moe_block() (state.t) */
+  MOE_DBG_TP_PARTIAL = 13 /* bf16 [rows, H]  this rank's partial-output buffer of the TP group (e_agg_g) */
 };
 int moe_get_debug(moe_handle h, int which, void *host_dst, size_t bytes);
 

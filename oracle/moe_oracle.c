@@ -361,3 +361,13 @@ int oracle_num_threads(void) {
   return 1;
 #endif
 }
+
+/* A launcher may export OMP_NUM_THREADS=1 to every child (torchrun does); the timed CPU baseline asks
+ * for the host's cores explicitly. */
+void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}

@@ -25,9 +25,15 @@ REF_SO = os.path.join(HERE, "_ref", "libref_moe.so")
 REF_MXFP4_SO = os.path.join(HERE, "_ref", "libref_mxfp4.so")
 
 
+def reference_dir() -> str:
+    """Where the reference checkout is looked for: MOE_REFERENCE_DIR, else a directory named
+    `reference` beside this repository."""
+    return os.environ.get("MOE_REFERENCE_DIR") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
 def build(quiet: bool = True) -> None:
     """Compile the checkers (the reference one only where its sources exist)."""
-    subprocess.run(["make", "-C", HERE, "all"], check=True,
+    subprocess.run(["make", "-C", HERE, "all", f"REF={reference_dir()}"], check=True,
                    stdout=subprocess.DEVNULL if quiet else None)
 
 
@@ -64,6 +70,9 @@ class Port:
 
     def threads(self) -> int:
         return int(self.lib.oracle_num_threads())
+
+    def set_threads(self, n: int) -> None:
+        self.lib.oracle_set_num_threads(int(n))
 
     def dequant(self, codes: np.ndarray, scales: np.ndarray) -> np.ndarray:
         codes = np.ascontiguousarray(codes)
@@ -144,6 +153,17 @@ class Port:
         return t, logits, idx, w, agg, xo
 
 
+def host_cores() -> int:
+    """Physical cores this process may run on (what the timed CPU baseline uses)."""
+    try:
+        import psutil
+        n = psutil.cpu_count(logical=False) or 0
+    except Exception:
+        n = 0
+    allowed = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    return max(1, min(n, allowed) if n else allowed)
+
+
 def reference_available() -> bool:
     return os.path.exists(REF_SO)
 
@@ -212,6 +232,9 @@ class Reference:
 
     def threads(self) -> int:
         return int(self.lib.ref_moe_num_threads())
+
+    def set_threads(self, n: int) -> None:
+        self.lib.ref_moe_set_num_threads(int(n))
 
     def prepare(self, t_bits: np.ndarray) -> int:
         """Dequantise the experts these rows will use (load-time work in the

@@ -264,4 +264,14 @@ int ref_moe_num_threads(void) {
 #endif
 }
 
+/* A launcher may export OMP_NUM_THREADS=1 to every child (torchrun does); the timed run asks for the
+ * host's cores explicitly. */
+void ref_moe_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 } // extern "C"

@@ -8,10 +8,15 @@ Tolerances (floating point path, stated once here):
     selected and first rejected logit is below 1e-5.
   * block output (bf16): mean relative error (mean|a-b| / mean|b|) <= 5e-3 and
     max|a-b| <= 2e-2 * max(1, rms(b)).  For outputs of unit scale or below (all
-    small fixtures) that is the literal 2e-2.  At the benchmark's weight scales
-    the layer output has rms ~37 and peaks near 200, where half a bf16 ulp is
-    already 0.5, so an absolute 2e-2 cannot be met by ANY bf16 result; the bound
-    is therefore taken relative to the output's rms.
+    small fixtures) that is the literal 2e-2, and check_output asserts the literal
+    bound there.  At the benchmark's weight scales the layer output has rms ~37
+    and peaks near 200, where half a bf16 ulp is already 0.5, so an absolute 2e-2
+    cannot be met by ANY bf16 result (check_output measures and prints that floor:
+    the error of the oracle's own output rounded to bf16); the bound is therefore
+    taken relative to the output's rms, and the raw figures are printed.
+  * a token whose selection differs from the oracle's (only allowed at a near-tie,
+    see above) is left out of the output comparison; every other row is compared,
+    and the number of such tokens is bounded (near_tie_budget).
   * the fp32 output kept before the final rounding: max|a-b| <= 1e-2 * max(1, rms(b))
     (the SwiGLU output feeds MLP2 as two e4m3 terms, i.e. with about 8 significant bits,
     as the reference GPU path does by rounding it to bf16).
@@ -43,27 +48,49 @@ def _load_case(name, synth):
     return layer, tokens, z
 
 
+def near_tie_budget(n_tokens):
+    """How many tokens may select differently from the oracle because of a near-tie at the cut."""
+    return max(2, n_tokens // 500)
+
+
 def check_selection(idx, ref_idx, ref_logits):
-    """Exact match, except tokens whose oracle logits are within 1e-5 at the cut."""
-    bad = np.nonzero((np.sort(idx, axis=1) != np.sort(ref_idx, axis=1)).any(axis=1))[0]
-    for t in bad:
+    """Exact match (same experts in the same order), except tokens where the oracle's own logits are within
+    1e-5 of each other at the place that differs (the cut, or two neighbours inside the selection); their
+    number is bounded.  Returns a mask of the rows that match exactly."""
+    same = (idx == ref_idx).all(axis=1)
+    k = idx.shape[1]
+    for t in np.nonzero(~same)[0]:
         s = np.sort(ref_logits[t])[::-1]
-        k = idx.shape[1]
-        assert s[k - 1] - s[k] < 1e-5, f"token {t}: selection differs with a clear logit gap {s[k-1]-s[k]}"
-    return len(bad)
+        gaps = s[:k] - s[1:k + 1]                     # between neighbours of the selection, the last one at the cut
+        assert gaps.min() < 1e-5, f"token {t}: selection differs with clear logit gaps {gaps}"
+    assert (~same).sum() <= near_tie_budget(len(idx)), f"{(~same).sum()} tokens select differently from the oracle"
+    return same
 
 
-def check_output(out_bits, out_f32, ref, synth):
+def check_output(out_bits, out_f32, ref, synth, rows=None, label=""):
+    """Both bounds on the rows of `rows` (a mask; default all).  Prints the raw figures."""
     got = synth.bf16_bits_to_f32(out_bits).astype(np.float64)
     ref = ref.astype(np.float64)
+    if rows is not None:
+        got, ref = got[rows], ref[rows]
+        out_f32 = None if out_f32 is None else out_f32[rows]
     err = np.abs(got - ref)
     mean_rel = err.mean() / max(np.abs(ref).mean(), 1e-30)
-    assert mean_rel <= 5e-3, f"mean relative error {mean_rel}"
     rms = np.sqrt((ref ** 2).mean())
-    assert err.max() <= 2e-2 * max(1.0, rms), f"max abs error {err.max()} at rms {rms}"
+    floor = np.abs(synth.bf16_bits_to_f32(synth.f32_to_bf16_bits(ref.astype(np.float32))).astype(np.float64) - ref).max()
+    msg = (f"{label} rows {len(ref)}: max abs {err.max():.4g} (bf16 rounding of the oracle itself: {floor:.4g}), "
+           f"rms(ref) {rms:.4g}, max abs / rms {err.max() / max(rms, 1e-30):.3g}, mean rel {mean_rel:.3g}")
+    e32max = None
     if out_f32 is not None:
-        e32 = np.abs(out_f32.astype(np.float64) - ref)
-        assert e32.max() <= 1e-2 * max(1.0, rms), f"fp32 output max abs error {e32.max()} at rms {rms}"
+        e32max = np.abs(out_f32.astype(np.float64) - ref).max()
+        msg += f", fp32 output max abs {e32max:.4g} ({e32max / max(rms, 1e-30):.3g} x rms)"
+    print(msg)
+    assert mean_rel <= 5e-3, f"mean relative error {mean_rel}"
+    assert err.max() <= 2e-2 * max(1.0, rms), f"max abs error {err.max()} at rms {rms}"
+    if rms <= 1.0:
+        assert err.max() <= 2e-2, f"max abs error {err.max()} above the literal 2e-2 at rms {rms}"
+    if e32max is not None:
+        assert e32max <= 1e-2 * max(1.0, rms), f"fp32 output max abs error {e32max} at rms {rms}"
     return mean_rel, err.max()
 
 
@@ -84,11 +111,9 @@ def test_golden_fixture(name, flags, pkg, synth):
         logits = blk.debug(pkg.DBG_LOGITS)
         np.testing.assert_allclose(logits, z["logits"], rtol=0, atol=2e-5 * max(1.0, np.abs(z["logits"]).max()))
         idx = blk.debug(pkg.DBG_TOPK_IDX)
-        nbad = check_selection(idx, z["topk_i"], z["logits"])
-        if nbad == 0:
-            assert np.array_equal(idx, z["topk_i"])
-            np.testing.assert_allclose(blk.debug(pkg.DBG_TOPK_W), z["topk_v"], rtol=2e-5, atol=1e-7)
-            check_output(out, blk.debug(pkg.DBG_OUT_F32), z["out"], synth)
+        same = check_selection(idx, z["topk_i"], z["logits"])
+        np.testing.assert_allclose(blk.debug(pkg.DBG_TOPK_W)[same], z["topk_v"][same], rtol=2e-5, atol=1e-7)
+        check_output(out, blk.debug(pkg.DBG_OUT_F32), z["out"], synth, rows=same, label=name)
     finally:
         blk.close()
 
@@ -159,9 +184,8 @@ def test_shapes_against_oracle(E, H, D, T, zipf, pkg, synth, port):
     for flags in (0, 1):
         blk, out = run_block(pkg, layer, tokens, flags=flags)
         try:
-            idx = blk.debug(pkg.DBG_TOPK_IDX)
-            if check_selection(idx, ref_i, ref_logits) == 0:
-                check_output(out, blk.debug(pkg.DBG_OUT_F32), ref_out, synth)
+            same = check_selection(blk.debug(pkg.DBG_TOPK_IDX), ref_i, ref_logits)
+            check_output(out, blk.debug(pkg.DBG_OUT_F32), ref_out, synth, rows=same)
         finally:
             blk.close()
 
@@ -174,9 +198,9 @@ def test_shape20b_64_tokens(pkg, synth, port):
     blk, out = run_block(pkg, layer, tokens)
     try:
         idx = blk.debug(pkg.DBG_TOPK_IDX)
-        assert check_selection(idx, ref_i, ref_logits) == 0
+        assert check_selection(idx, ref_i, ref_logits).all()
         assert np.array_equal(idx, ref_i)
-        mean_rel, max_abs = check_output(out, blk.debug(pkg.DBG_OUT_F32), ref_out, synth)
+        mean_rel, max_abs = check_output(out, blk.debug(pkg.DBG_OUT_F32), ref_out, synth, label="20B shape T=64")
         print(f"20B shape T=64: mean rel {mean_rel:.3e}, max abs {max_abs:.3e}, ref rms {np.sqrt((ref_out**2).mean()):.2f}")
         # the plain CUDA-core GEMM (fp16 operands) and the tensor-core GEMM agree to bf16 precision
         out_simt = synth.bf16_bits_to_f32(blk.forward_host(0, tokens, flags=pkg.FWD_SIMT_GEMM))
@@ -186,12 +210,47 @@ def test_shape20b_64_tokens(pkg, synth, port):
         blk.close()
 
 
-def test_full_size_properties(pkg, synth):
+@pytest.fixture(scope="module")
+def layer_120b(synth):
+    """The benchmark's layer: 120B shape, seed 0 (about a minute of host time, so it is made once)."""
+    return synth.make_layer(128, 2880, 2880, seed=0)
+
+
+@pytest.mark.parametrize("zipf", [None, 1.2], ids=["uniform", "zipf1.2"])
+def test_headline_shape_sampled_rows_against_oracle(zipf, layer_120b, pkg, synth, port):
+    """The configuration every benchmark number is quoted on (120B shape, 1856 rows, seed 0), with uniform
+    and with Zipf(1.2) routing: the whole batch runs on the GPU, and 64 sampled rows are compared with the
+    oracle run on those rows alone (a row's result depends on no other row: run.cpp:657-748 is a loop over
+    tokens)."""
+    E, H, D, T = 128, 2880, 2880, 1856
+    layer = dict(layer_120b)
+    if zipf is not None:
+        layer["router_b"] = synth.zipf_router_bias(E, zipf)
+    tokens = synth.make_tokens(T, H, seed=0)
+    sample = np.sort(np.random.default_rng(2).choice(T, size=64, replace=False))
+    ref_logits, ref_i, ref_w, ref_out = port.moe_layer(layer, tokens[sample])
+    blk, out = run_block(pkg, layer, tokens, keep_f32=True)
+    try:
+        logits = blk.debug(pkg.DBG_LOGITS)[sample]
+        np.testing.assert_allclose(logits, ref_logits, rtol=0, atol=2e-5 * max(1.0, np.abs(ref_logits).max()))
+        same = check_selection(blk.debug(pkg.DBG_TOPK_IDX)[sample], ref_i, ref_logits)
+        np.testing.assert_allclose(blk.debug(pkg.DBG_TOPK_W)[sample][same], ref_w[same], rtol=2e-5, atol=1e-7)
+        check_output(out[sample], blk.debug(pkg.DBG_OUT_F32)[sample], ref_out, synth, rows=same,
+                     label=f"120B shape T={T} {'zipf' if zipf else 'uniform'}")
+        counts = blk.debug(pkg.DBG_COUNTS)
+        assert counts.sum() == 4 * T
+        if zipf is not None:
+            assert counts.max() > T // 2 and (counts == 0).any()   # the skew the case is about
+    finally:
+        blk.close()
+
+
+def test_full_size_properties(layer_120b, pkg, synth):
     """120B-shape layer at 1856 rows: properties that need no CPU run.
     Row order does not matter (a permuted batch gives the permuted output, bit
     for bit), repeated rows give repeated outputs, and two runs agree."""
     E, H, D, T = 128, 2880, 2880, 1856
-    layer = synth.make_layer(E, H, D, seed=0)
+    layer = layer_120b
     tokens = synth.make_tokens(T, H, seed=0)
     tokens[100] = tokens[7]
     tokens[1855] = tokens[7]
@@ -303,16 +362,15 @@ def check_block_form(pkg, synth, port, layer, x_bits, gain_bits, ref=None):
         diff = t_got.astype(np.int32) - t_want.astype(np.int32)
         assert np.abs(diff).max() <= 1, "normalised rows differ by more than one bf16 ulp"
         assert (diff != 0).mean() <= 2e-3, f"{(diff != 0).mean():.2%} of the normalised rows differ"
-        nbad = check_selection(blk.debug(pkg.DBG_TOPK_IDX), idx_ref, logits_ref)
+        same = check_selection(blk.debug(pkg.DBG_TOPK_IDX), idx_ref, logits_ref)
         got = synth.bf16_bits_to_f32(d_x.cpu().numpy().view(np.uint16)).astype(np.float64)
-        if nbad == 0:
-            err = np.abs(got - xo_ref)
-            rms = np.sqrt((agg_ref.astype(np.float64) ** 2).mean())
-            bound = 2e-2 * max(1.0, rms) + 2.0 ** -8 * np.abs(xo_ref)
-            assert (err <= bound).all(), f"max excess {(err - bound).max()}"
-            upd = np.abs((got - x) - agg_ref).mean() / max(np.abs(agg_ref).mean(), 1e-30)
-            # the update itself, seen through the rounding of the sum: coarse, but catches a missing residual or bias
-            assert upd <= 0.1, f"mean relative error of the update {upd}"
+        err = np.abs(got - xo_ref)[same]
+        rms = np.sqrt((agg_ref[same].astype(np.float64) ** 2).mean())
+        bound = (2e-2 * max(1.0, rms) + 2.0 ** -8 * np.abs(xo_ref))[same]
+        assert (err <= bound).all(), f"max excess {(err - bound).max()}"
+        upd = np.abs((got - x) - agg_ref)[same].mean() / max(np.abs(agg_ref[same]).mean(), 1e-30)
+        # the update itself, seen through the rounding of the sum: coarse, but catches a missing residual or bias
+        assert upd <= 0.1, f"mean relative error of the update {upd}"
     finally:
         blk.close()
 

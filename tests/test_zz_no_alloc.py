@@ -58,6 +58,51 @@ def test_route_static_matches_regular_path_twice(pkg, synth):
         blk.close()
 
 
+def test_route_static_sliced_to_fit_after_a_larger_call(pkg, synth, port):
+    """A batch whose usual number of k-slices does not fit the fixed array (256 experts x 2368 rows: four slices
+    of 606 208 floats against 2 097 152) is routed with fewer, longer slices.  It runs right after a larger batch
+    that filled more of the array, and both are checked against the CPU oracle as well as against the regular
+    entry point.  The call must leave the amount of free device memory as it found it."""
+    import torch
+    E, H, D = 256, 512, 64
+    layer = synth.make_layer(E, H, D, seed=95)
+    blk = pkg.MoeBlock(H, D, E, max_rows=4000)
+    try:
+        blk.load_layer(0, layer)
+        stream = torch.cuda.current_stream().cuda_stream
+        for call, T in enumerate((4000, 2368)):
+            tokens = synth.make_tokens(T, H, seed=96 + call)
+            ref_logits, ref_i, ref_w, _ = port.moe_layer(layer, tokens)
+            d_t = torch.from_numpy(tokens.view(np.int16)).cuda()
+            d_o = torch.empty_like(d_t)
+            blk.forward(0, d_t.data_ptr(), T, d_o.data_ptr(), 0, stream)
+            torch.cuda.synchronize()
+            reg_logits, reg_idx = blk.debug(pkg.DBG_LOGITS), blk.debug(pkg.DBG_TOPK_IDX)
+            logits = torch.full((T, E), float("nan"), dtype=torch.float32, device="cuda")
+            idx = torch.full((T, 4), -1, dtype=torch.int32, device="cuda")
+            w = torch.full((T, 4), float("nan"), dtype=torch.float32, device="cuda")
+            torch.cuda.synchronize()
+            free_before = torch.cuda.mem_get_info()[0]
+            blk.route_static(0, d_t.data_ptr(), T, logits.data_ptr(), idx.data_ptr(), w.data_ptr(), stream)
+            torch.cuda.synchronize()
+            blk.synchronize()
+            assert torch.cuda.mem_get_info()[0] == free_before, "moe_route_static changed the free device memory"
+            got, got_i, got_w = logits.cpu().numpy(), idx.cpu().numpy(), w.cpu().numpy()
+            tol = 2e-5 * max(1.0, float(np.abs(ref_logits).max()))
+            np.testing.assert_allclose(got, ref_logits, rtol=0, atol=tol)
+            np.testing.assert_allclose(got, reg_logits, rtol=0, atol=tol)
+            srt = np.sort(ref_logits, axis=1)[:, ::-1]
+            near_tie = (srt[:, :4] - srt[:, 1:5]).min(axis=1) < 1e-5
+            for other in (ref_i, reg_idx):
+                differ = (got_i != other).any(axis=1)
+                assert (near_tie | ~differ).all(), "selection differs from the oracle where its logits are clearly apart"
+                assert differ.sum() <= max(2, T // 500)
+            ok = (got_i == ref_i).all(axis=1)
+            np.testing.assert_allclose(got_w[ok], ref_w[ok], rtol=2e-5, atol=1e-7)
+    finally:
+        blk.close()
+
+
 def test_route_static_rejects_oversize(pkg, synth):
     import torch
     E, H, D = 256, 64, 64

@@ -26,7 +26,8 @@ def main():
     E, H, D, rows_local = 16, 256, 320, 50
     layer = pkg.synth.make_layer(E, H, D, seed=7)
     union = pkg.synth.make_tokens(rows_local * world, H, seed=8)
-    mine = union[rank * rows_local:(rank + 1) * rows_local]
+    sl_mine = slice(rank * rows_local, (rank + 1) * rows_local)
+    mine = union[sl_mine]
     blk = pkg.MoeBlock(H, D, E, max_rows=rows_local * world, tp_size=world, tp_rank=rank, device=local)
     blk.load_layer(0, layer)
     tp.attach_group(blk, rank)
@@ -53,6 +54,37 @@ def main():
     blk.synchronize()
     blk.rows = rows_local * world
     assert np.array_equal(blk.debug(pkg.DBG_GATHER), union), "all-gather buffer differs from the union of the ranks' rows"
+    # The three steps as separate calls (the reference's own order: ring_allgather_rows_bf16, the MLPs into
+    # e_agg_g, the owner-slice reduce-scatter; getp_run.cpp:2958-3246), four times in a row on different rows,
+    # so that buffers and epoch flags are reused while their contents change.  The reduce-scatter's output must
+    # be, bit for bit, the fp32 sum in rank order of the ranks' bf16 partials, and match the oracle.
+    gather_ptr, partial_ptr = blk.tp_buffer(pkg.TP_BUF_GATHER), blk.tp_buffer(pkg.TP_BUF_PARTIAL)
+    port = oracle.Port()
+    unions = [pkg.synth.make_tokens(rows_local * world, H, seed=30 + it) for it in range(4)]
+    d_ins = [torch.from_numpy(np.ascontiguousarray(u[sl_mine]).view(np.int16).copy()).cuda() for u in unions]
+    d_rss = [torch.zeros_like(d) for d in d_ins]
+    for it in range(4):                       # no host synchronisation between the steps or the rounds
+        blk.tp_allgather(d_ins[it].data_ptr(), rows_local, stream)
+        blk.forward(0, gather_ptr, rows_local * world, partial_ptr, 0, stream)
+        blk.tp_reduce_scatter(rows_local, d_rss[it].data_ptr(), stream)
+    torch.cuda.synchronize()
+    blk.synchronize()
+    blk.rows = rows_local * world
+    assert np.array_equal(blk.debug(pkg.DBG_GATHER), unions[-1]), "gathered rows differ from the union"
+    my_partial = torch.from_numpy(blk.debug(pkg.DBG_TP_PARTIAL).view(np.int16).copy())
+    parts = [torch.empty_like(my_partial) for _ in range(world)]
+    dist.all_gather(parts, my_partial)
+    acc = np.zeros((rows_local, H), dtype=np.float32)
+    for r in range(world):                    # fp32 adds in rank order, as the kernel does
+        acc = acc + pkg.synth.bf16_bits_to_f32(parts[r].numpy().view(np.uint16)[sl_mine])
+    assert np.array_equal(d_rss[-1].cpu().numpy().view(np.uint16), pkg.synth.f32_to_bf16_bits(acc)), \
+        "reduce-scatter is not the rank-ordered fp32 sum of the ranks' bf16 partials"
+    for it in range(4):
+        _, _, _, ref_it = port.moe_layer(layer, unions[it])
+        ref_rows = ref_it[sl_mine].astype(np.float64)
+        e = np.abs(pkg.synth.bf16_bits_to_f32(d_rss[it].cpu().numpy().view(np.uint16)).astype(np.float64) - ref_rows)
+        r_rms = max(1.0, float(np.sqrt((ref_rows ** 2).mean())))
+        assert e.mean() / np.abs(ref_rows).mean() <= 5e-3 and e.max() <= 2e-2 * r_rms, (it, e.mean(), e.max(), r_rms)
     # the reference's calling form over the group: x <- x + MoE(rmsnorm(x) * gain) on each rank's rows
     x_bits, gain_bits = pkg.synth.make_residual(rows_local * world, H, seed=9)
     xf, gf = pkg.synth.bf16_bits_to_f32(x_bits), pkg.synth.bf16_bits_to_f32(gain_bits)
