@@ -35,7 +35,7 @@ EXPORTS = [
     "moe_last_error", "moe_strerror", "moe_launch_count", "moe_profile_enable", "moe_profile_collect",
     "moe_route_static", "moe_block", "moe_forward_host_submit", "moe_forward_host_wait",
     "moe_quantize_mxfp4", "moe_load_layer_f32", "moe_tp_export", "moe_tp_attach_ipc", "moe_tp_buffer", "moe_tp_attach_ptr",
-    "moe_tp_forward", "moe_tp_forward_host", "moe_tp_allgather", "moe_tp_reduce_scatter",
+    "moe_tp_forward", "moe_tp_forward_host", "moe_tp_allgather", "moe_tp_reduce_scatter", "moe_tp_allreduce",
 ]
 TP_BUF_GATHER, TP_BUF_PARTIAL, TP_BUF_FLAGS, TP_BUF_TOPK_IDX, TP_BUF_TOPK_W = range(5)
 TP_N_BUFS = 5
@@ -95,6 +95,7 @@ def lib() -> C.CDLL:
         L.moe_tp_forward_host.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_uint]
         L.moe_tp_allgather.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
         L.moe_tp_reduce_scatter.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
+        L.moe_tp_allreduce.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
         L.moe_forward_host_submit.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_uint,
                                               C.POINTER(C.c_longlong)]
         L.moe_forward_host_wait.argtypes = [C.c_void_p, C.c_longlong]
@@ -274,6 +275,10 @@ class MoeBlock:
 
     def tp_reduce_scatter(self, rows_local: int, out_ptr: int, stream: int = 0):
         self._check(self.L.moe_tp_reduce_scatter(self.h, rows_local, C.c_void_p(out_ptr), C.c_void_p(stream)))
+
+    def tp_allreduce(self, buf_ptr: int, n_elems: int, stream: int = 0):
+        """In place: bf16 buffer <- sum over the ranks of the group (fp32 adds in rank order)."""
+        self._check(self.L.moe_tp_allreduce(self.h, C.c_void_p(buf_ptr), n_elems, C.c_void_p(stream)))
 
     def debug(self, which: int) -> np.ndarray:
         T, E, K, H = self.rows, self.E, self.K, self.H

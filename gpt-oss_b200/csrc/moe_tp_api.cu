@@ -140,6 +140,30 @@ int moe_tp_reduce_scatter(moe_handle c, int rows_local, void *out_local, void *s
   return MOE_OK;
 }
 
+int moe_tp_allreduce(moe_handle c, void *buf_dev, size_t n_elems, void *stream) {
+  if (!c || !buf_dev) return MOE_ERR_INVALID;
+  if (n_elems == 0) return MOE_OK;
+  if (n_elems % 8 != 0 || n_elems > static_cast<size_t>(c->max_rows) * c->H)
+    return tp_fail(c, MOE_ERR_INVALID, "moe_tp_allreduce: %zu elements (must be a multiple of 8 and at most max_rows * H = %zu)",
+                   n_elems, static_cast<size_t>(c->max_rows) * c->H);
+  int rc = check_tp_call(c, 1, "moe_tp_allreduce");
+  if (rc != MOE_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int tp = c->cfg.tp_size, rank = c->cfg.tp_rank;
+  // 1. every rank has finished reading the partial buffers of the previous collective; 2. this rank's values are
+  // in its partial buffer; 3. every rank's values are in place; 4. sum all ranks' buffers in rank order.
+  ++c->tp_epoch;
+  launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, 0, c->tp_epoch, c->status, s);
+  if (cudaMemcpyAsync(c->tp_partial, buf_dev, n_elems * 2, cudaMemcpyDeviceToDevice, s) != cudaSuccess)
+    return tp_fail(c, MOE_ERR_CUDA, "moe_tp_allreduce: staging copy failed");
+  ++c->tp_epoch_rs;
+  launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, 1, c->tp_epoch_rs, c->status, s);
+  launch_tp_sum_all(c->peers, tp, n_elems, static_cast<__nv_bfloat16 *>(buf_dev), c->sm_count, s);
+  c->launches += 3;
+  if (cudaGetLastError() != cudaSuccess) return tp_fail(c, MOE_ERR_CUDA, "moe_tp_allreduce: launch failed");
+  return MOE_OK;
+}
+
 int moe_tp_forward(moe_handle c, int layer, const void *t_local, int rows_local, void *out_local, unsigned flags,
                    void *stream) {
   if (!c || !t_local || !out_local) return MOE_ERR_INVALID;

@@ -286,7 +286,6 @@ build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ cou
                    unsigned int *status) {
   __shared__ int s_red[2][8];
   __shared__ int s_warp[8];
-  __shared__ int s_running;
   const int e = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   // exclusive prefix over experts below e: rows and token tiles
@@ -302,7 +301,6 @@ build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ cou
     my_tiles += __shfl_xor_sync(0xffffffffu, my_tiles, off);
   }
   if (lane == 0) { s_red[0][warp] = my_rows; s_red[1][warp] = my_tiles; }
-  if (tid == 0) s_running = 0;
   __syncthreads();
   int off = 0, tiles_before = 0;
 #pragma unroll
@@ -315,22 +313,39 @@ build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ cou
     if (e == E - 1) { offsets[E] = off + cnt; tile_base[E] = tiles_before + ntt; }
   }
 
-  // stable compaction in ascending token order
-  for (int base = 0; base < T; base += blockDim.x) {
-    const int t = base + tid;
-    int hit = -1;
-    if (t < T)
-      for (int k = 0; k < K; ++k)
-        if (topk_idx[static_cast<size_t>(t) * K + k] == e) { hit = k; break; }
+  // Stable compaction in ascending token order.  Warp w owns the contiguous token range [w*per, (w+1)*per):
+  // a first walk counts the range's hits with ballots, one block-wide barrier turns the eight counts into
+  // starting positions, a second walk (the selections are still in L1) writes the rows.  No barrier per step.
+  const int per = ((T + 7) / 8 + 31) / 32 * 32;       // tokens per warp, whole ballot steps
+  const int t_begin = warp * per, t_end = min(T, t_begin + per);
+  auto hit_of = [&](int t) -> int {
+    if (t >= t_end) return -1;
+    if (K == 4) {                                      // the usual case: one 16-byte load
+      const int4 v = __ldg(reinterpret_cast<const int4 *>(topk_idx) + t);
+      return v.x == e ? 0 : v.y == e ? 1 : v.z == e ? 2 : v.w == e ? 3 : -1;
+    }
+    for (int k = 0; k < K; ++k)
+      if (topk_idx[static_cast<size_t>(t) * K + k] == e) return k;
+    return -1;
+  };
+  int mine = 0;
+  for (int t0 = t_begin; t0 < t_end; t0 += 32) mine += __popc(__ballot_sync(0xffffffffu, hit_of(t0 + lane) >= 0));
+  if (lane == 0) s_warp[warp] = mine;
+  __syncthreads();
+  int before = 0, total_hits = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    before += i < warp ? s_warp[i] : 0;
+    total_hits += s_warp[i];
+  }
+  for (int t0 = t_begin; t0 < t_end; t0 += 32) {
+    const int t = t0 + lane;
+    const int hit = hit_of(t);
     const unsigned m = __ballot_sync(0xffffffffu, hit >= 0);
-    if (lane == 0) s_warp[warp] = __popc(m);
-    __syncthreads();
-    int before = s_running;
-    for (int i = 0; i < warp; ++i) before += s_warp[i];
     if (hit >= 0) {
-      const int r = off + before + __popc(m & ((1u << lane) - 1u));
       const int pos = before + __popc(m & ((1u << lane) - 1u));
       if (pos < cnt) {
+        const int r = off + pos;
         row_token[r] = t;
         // where the row's high term goes in the quantised activations: token tile, then 2 rows per token
         row_slot[r] = (tiles_before + pos / kTokTile) * kTileM + 2 * (pos % kTokTile);
@@ -339,15 +354,9 @@ build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ cou
         atomicOr(status, ST_BAD_INDEX);
       }
     }
-    __syncthreads();
-    if (tid == 0) {
-      int tot = 0;
-      for (int i = 0; i < 8; ++i) tot += s_warp[i];
-      s_running += tot;
-    }
-    __syncthreads();
+    before += __popc(m);
   }
-  if (tid == 0 && s_running != cnt) atomicOr(status, ST_BAD_INDEX);
+  if (tid == 0 && total_hits != cnt) atomicOr(status, ST_BAD_INDEX);
 
   // work items: one per (token tile of kTokTile rows, block of kTileN weight rows); items that share a
   // weight block are adjacent so that block is fetched from HBM once and re-read from L2.  Single blocks
@@ -432,9 +441,9 @@ quantize_rows_kernel(const __nv_bfloat16 *__restrict__ t, const int *__restrict_
   int e = static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu) - 127 - 7;
   e = max(-120, min(e, 120));
   const float inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);  // 2^-e
-  // activation tiles: [tile][k slice][128 rows][128 bytes]; 8 elements never straddle a slice
+  // activation tiles: [tile][k slice][16-byte column][128 rows][16 bytes]; 8 elements never straddle a column
   const int n_kc = (H + kChunkK - 1) / kChunkK;
-  uint8_t *tile_hi = xq + (static_cast<size_t>(tile) * n_kc * kTileM + i2) * kChunkK;
+  uint8_t *tile_hi = xq + static_cast<size_t>(tile) * n_kc * (kTileM * kChunkK) + i2 * 16;
 #pragma unroll
   for (int u = 0; u < kQrVec; ++u) {
     const int c = threadIdx.x + u * kQrThreads;
@@ -462,9 +471,10 @@ quantize_rows_kernel(const __nv_bfloat16 *__restrict__ t, const int *__restrict_
       const uint32_t d2 = __nv_cvt_float2_to_fp8x2(make_float2(rs[2], rs[3]), __NV_SATFINITE, __NV_E4M3);
       l8[g] = c2 | (d2 << 16);
     }
-    uint8_t *dst = tile_hi + static_cast<size_t>(c >> 4) * (kTileM * kChunkK) + (c & 15) * 8;  // slice c/16, byte 8*(c%16)
+    // slice c/16; inside it 16-byte column (c%16)/2, then the row, then byte 8*(c%2)
+    uint8_t *dst = tile_hi + static_cast<size_t>(c >> 4) * (kTileM * kChunkK) + ((c & 15) >> 1) * kActColBytes + (c & 1) * 8;
     *reinterpret_cast<uint2 *>(dst) = make_uint2(h8[0], h8[1]);
-    *reinterpret_cast<uint2 *>(dst + kChunkK) = make_uint2(l8[0], l8[1]);                      // the low row follows
+    *reinterpret_cast<uint2 *>(dst + 16) = make_uint2(l8[0], l8[1]);                           // the low row follows
   }
   if (threadIdx.x < 2) {
     const int rr = i2 + threadIdx.x;  // row inside the tile: even = high, odd = low
@@ -520,7 +530,7 @@ void launch_gather_rows(const __nv_bfloat16 *t, const int *row_token, const int 
 // order and rounding of run.cpp:678 / :738-741.  GPU counterpart:
 // reduce_tokenwise_expert_outputs_bf16_bf16wts (kernels/moe.hpp:700-730).
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 combine_kernel(const __half *__restrict__ y, const int *__restrict__ topk_idx, const float *__restrict__ topk_w,
                const int *__restrict__ pair_row, int T, int H, int K, __nv_bfloat16 *__restrict__ out_bf16,
                float *__restrict__ out_f32, int tp, TpPeers peers, int rows_local, int rank,
@@ -544,32 +554,43 @@ combine_kernel(const __half *__restrict__ y, const int *__restrict__ topk_idx, c
       a = row[j]; row[j] = row[j - 1]; row[j - 1] = a;
       float f = wt[j]; wt[j] = wt[j - 1]; wt[j - 1] = f;
     }
-  for (int i = threadIdx.x; i < H / 4; i += blockDim.x) {
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  // 16 bytes (8 values) per thread and expert row: the K loads of an iteration are in flight together
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
     for (int k = 0; k < K; ++k) {
-      const uint2 raw = __ldg(reinterpret_cast<const uint2 *>(y + static_cast<size_t>(row[k]) * H) + i);
-      const float2 v01 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
-      const float2 v23 = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
-      const float4 v = make_float4(v01.x, v01.y, v23.x, v23.y);
-      acc.x = __fadd_rn(acc.x, __fmul_rn(v.x, wt[k]));
-      acc.y = __fadd_rn(acc.y, __fmul_rn(v.y, wt[k]));
-      acc.z = __fadd_rn(acc.z, __fmul_rn(v.z, wt[k]));
-      acc.w = __fadd_rn(acc.w, __fmul_rn(v.w, wt[k]));
+      const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(y + static_cast<size_t>(row[k]) * H) + i);
+      const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 v = __half22float2(*reinterpret_cast<const __half2 *>(&w4[j]));
+        acc[2 * j] = __fadd_rn(acc[2 * j], __fmul_rn(v.x, wt[k]));
+        acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], __fmul_rn(v.y, wt[k]));
+      }
     }
-    if (out_f32 != nullptr) reinterpret_cast<float4 *>(out_f32 + static_cast<size_t>(t) * H)[i] = acc;
+    if (out_f32 != nullptr) {
+      float4 *o = reinterpret_cast<float4 *>(out_f32 + static_cast<size_t>(t) * H) + 2 * i;
+      o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    }
     if (residual != nullptr) {  // x += block output (accumulate_kernel_bf16, kernels/other_kernels.hpp:18-37), one rounding
-      const uint2 r = __ldg(reinterpret_cast<const uint2 *>(residual + static_cast<size_t>(t) * H) + i);
-      acc.x += __uint_as_float(r.x << 16);
-      acc.y += __uint_as_float(r.x & 0xffff0000u);
-      acc.z += __uint_as_float(r.y << 16);
-      acc.w += __uint_as_float(r.y & 0xffff0000u);
+      const uint4 r = __ldg(reinterpret_cast<const uint4 *>(residual + static_cast<size_t>(t) * H) + i);
+      const uint32_t r4[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[2 * j] += __uint_as_float(r4[j] << 16);
+        acc[2 * j + 1] += __uint_as_float(r4[j] & 0xffff0000u);
+      }
     }
     if (out_bf16 != nullptr) {
-      const __nv_bfloat162 a = __floats2bfloat162_rn(acc.x, acc.y), b = __floats2bfloat162_rn(acc.z, acc.w);
-      uint2 o;
-      o.x = *reinterpret_cast<const uint32_t *>(&a);
-      o.y = *reinterpret_cast<const uint32_t *>(&b);
-      reinterpret_cast<uint2 *>(out_bf16 + static_cast<size_t>(t) * H)[i] = o;
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const __nv_bfloat162 b = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+        o[j] = *reinterpret_cast<const uint32_t *>(&b);
+      }
+      reinterpret_cast<uint4 *>(out_bf16 + static_cast<size_t>(t) * H)[i] = make_uint4(o[0], o[1], o[2], o[3]);
     }
   }
 }
@@ -579,7 +600,7 @@ void launch_combine(const __half *y, const int *topk_idx, const float *topk_w, c
                     int rows_local, int rank, const __nv_bfloat16 *residual) {
   TpPeers pv = {};
   if (tp > 0 && peers != nullptr) pv = *peers;
-  combine_kernel<<<T, 256, 0, s>>>(y, topk_idx, topk_w, pair_row, T, H, K, out_bf16, out_f32, tp, pv, rows_local, rank,
+  combine_kernel<<<T, 128, 0, s>>>(y, topk_idx, topk_w, pair_row, T, H, K, out_bf16, out_f32, tp, pv, rows_local, rank,
                                    residual);
 }
 

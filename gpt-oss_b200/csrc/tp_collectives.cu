@@ -156,4 +156,11 @@ void launch_tp_reduce_scatter_pull(const TpPeers &peers, int tp, int rank, int r
                                                                     reinterpret_cast<uint4 *>(out));
 }
 
+// All-reduce read half: out[i] = bf16( sum over ranks of peer_partial[r][i] ) for the first n_elems elements.
+void launch_tp_sum_all(const TpPeers &peers, int tp, size_t n_elems, __nv_bfloat16 *out, int sm_count, cudaStream_t s) {
+  const size_t n_vec = n_elems / 8;
+  const int blocks = static_cast<int>(std::min<size_t>((n_vec + 255) / 256, static_cast<size_t>(sm_count) * 4));
+  tp_reduce_scatter_pull_kernel<<<std::max(blocks, 1), 256, 0, s>>>(peers, tp, 0, n_vec, reinterpret_cast<uint4 *>(out));
+}
+
 }  // namespace moe

@@ -184,6 +184,13 @@ int moe_tp_forward_host(moe_handle h, int layer, const void *t_local_host, int r
 int moe_tp_allgather(moe_handle h, const void *src_local_dev, int rows_local, void *stream);
 int moe_tp_reduce_scatter(moe_handle h, int rows_local, void *out_local_dev, void *stream);
 
+/* Replaces ring_allreduce_sum_bf16 (getp-csrc/tp_ring.hpp:253-331) and the token-wise all-reduce of moe_gpu
+ * (getp_run.cpp:2834-2874): after the call buf_dev (bf16, n_elems elements, the same count on every rank of
+ * the group) holds the element-wise sum over the ranks, added in fp32 in rank order and rounded once, so every
+ * rank ends with the same bits.  n_elems must be a multiple of 8 and at most max_rows * hidden_dim (the values
+ * travel through the handle's partial-output buffer).  Every rank calls; stream-ordered, peer waits bounded. */
+int moe_tp_allreduce(moe_handle h, void *buf_dev, size_t n_elems, void *stream);
+
 /* No counterpart in the reference.  Router + top-k + softmax for a caller that must not reach
  * the CUDA allocator when it needs a routing decision (its memory was handed out once by a pool
  * that owns the device, or it cannot afford the device-wide synchronisation inside cudaMalloc).

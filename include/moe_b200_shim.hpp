@@ -5,6 +5,9 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <atomic>
+#include <chrono>
+#include <cstdint>
 #include <cstdio>
 #include <cstdlib>
 
@@ -102,10 +105,121 @@ inline void moe_gpu_b200_block(const TPGroup &tp, int layer_idx, void *x_rows, c
   if (rc != MOE_OK) moe_b200_die(h, "moe_gpu_b200_block", rc);
 }
 
-// ring_allgather_rows_bf16 (getp-csrc/tp_ring.hpp:70-118): the gathered [TP*R_local, C] rows end up in
-// the handle's gather buffer (moe_tp_buffer(h, MOE_TP_BUF_GATHER)); C must be the hidden size.
-inline void ring_allgather_rows_bf16(const void *my_src, int R_local, const TPGroup &tp, cudaStream_t s) {
+// ring_allgather_rows_bf16 (getp-csrc/tp_ring.hpp:70-118), the reference's full signature.  Every rank's
+// [R_local, C] rows end up, in rank order, in `my_dst` ([TP*R_local, C]).  The library gathers by peer stores
+// into the handle's own symmetric buffer (moe_tp_buffer(h, MOE_TP_BUF_GATHER)); when `my_dst` is another
+// buffer the rows are copied there on the same stream.  `peer_dst_bases` is what the reference's ring writes
+// into on the other ranks; here every rank fills its own destination, so the argument is accepted and not
+// used.  C must be the hidden size the handle was created with.
+inline void ring_allgather_rows_bf16(void *my_dst, const void *my_src, int R_local, int C, void *const peer_dst_bases[],
+                                     const TPGroup &tp, cudaStream_t s) {
+  (void)peer_dst_bases;
+  if (R_local == 0 || C == 0 || tp.tp_size <= 0) return;
   moe_handle h = moe_b200_handles()[tp.world_rank];
-  const int rc = moe_tp_allgather(h, my_src, R_local, s);
+  int rc = moe_tp_allgather(h, my_src, R_local, s);
   if (rc != MOE_OK) moe_b200_die(h, "ring_allgather_rows_bf16", rc);
+  void *gathered = nullptr;
+  rc = moe_tp_buffer(h, MOE_TP_BUF_GATHER, &gathered);
+  if (rc != MOE_OK) moe_b200_die(h, "ring_allgather_rows_bf16", rc);
+  if (my_dst != nullptr && my_dst != gathered &&
+      cudaMemcpyAsync(my_dst, gathered, static_cast<size_t>(tp.tp_size) * R_local * C * 2, cudaMemcpyDeviceToDevice, s) != cudaSuccess)
+    moe_b200_die(h, "ring_allgather_rows_bf16: copy to my_dst", MOE_ERR_CUDA);
 }
+
+// ring_allreduce_sum_bf16 (getp-csrc/tp_ring.hpp:253-331): after the call buf_local holds the element-wise
+// sum over the ranks of the group.  peer_bases and d_recv (the reference's peer pointers and receive tile) are
+// accepted and not used: the values travel through the handle's symmetric partial-output buffer.
+inline void ring_allreduce_sum_bf16(void *buf_local, void *const peer_bases[], size_t N_elems, void *d_recv,
+                                    const TPGroup &tp, cudaStream_t s) {
+  (void)peer_bases;
+  (void)d_recv;
+  if (tp.tp_size <= 1 || N_elems == 0) return;
+  moe_handle h = moe_b200_handles()[tp.world_rank];
+  const int rc = moe_tp_allreduce(h, buf_local, N_elems, s);
+  if (rc != MOE_OK) moe_b200_die(h, "ring_allreduce_sum_bf16", rc);
+}
+
+// tp_group_barrier (getp-csrc/nccl.hpp:100-137): host barrier of the threads that drive one TP group.  The
+// library's own calls need none (peers meet through device-side epoch flags); it is kept for callers that
+// synchronise their threads around other work.  Unlike the reference's, the wait is bounded: a group that does
+// not complete within 30 s aborts with a message instead of spinning forever.
+#ifndef MAX_TP_GROUPS
+#define MAX_TP_GROUPS 8
+#endif
+struct TPBarrierState {
+  std::atomic<int> count[MAX_TP_GROUPS];
+  std::atomic<uint64_t> epoch[MAX_TP_GROUPS];
+  TPBarrierState() {
+    for (int i = 0; i < MAX_TP_GROUPS; ++i) { count[i].store(0); epoch[i].store(0); }
+  }
+};
+inline TPBarrierState &tp_barrier_state() {
+  static TPBarrierState st;
+  return st;
+}
+inline void tp_group_barrier(const TPGroup &tp) {
+  TPBarrierState &st = tp_barrier_state();
+  const int gid = tp.group_id % MAX_TP_GROUPS;
+  const uint64_t seen = st.epoch[gid].load(std::memory_order_acquire);
+  if (st.count[gid].fetch_add(1, std::memory_order_acq_rel) + 1 == tp.tp_size) {
+    st.count[gid].store(0, std::memory_order_release);
+    st.epoch[gid].fetch_add(1, std::memory_order_acq_rel);
+    return;
+  }
+  const auto t0 = std::chrono::steady_clock::now();
+  for (unsigned spin = 0; st.epoch[gid].load(std::memory_order_acquire) == seen; ++spin) {
+    if ((spin & 0xffffu) == 0xffffu && std::chrono::steady_clock::now() - t0 > std::chrono::seconds(30)) {
+      fprintf(stderr, "tp_group_barrier: group %d did not complete within 30 s\n", tp.group_id);
+      abort();
+    }
+  }
+}
+
+// The part of the reference's per-device model state that its MoE call reads (GPUTransformer,
+// getp_run.cpp:206-212, with the same field names), so that forward_batch_gpu-style callers compile against
+// moe_gpu / moe_gpu_120b unchanged.  A caller that keeps the reference's own, larger structs defines
+// MOE_B200_SHIM_NO_TYPES and uses moe_gpu_b200_block() directly.
+#ifndef MOE_B200_SHIM_NO_TYPES
+struct Config {              // run.cpp:25-45 (the fields the MoE block reads)
+  int hidden_dim;
+  int intermediate_dim;
+  int n_experts;
+  int experts_per_token;
+  int n_layers;
+  float swiglu_limit;
+};
+struct GPUTransformerWeights {  // getp_run.cpp:48-81
+  void *rms_ffn_w;              // bf16 [n_layers, hidden_dim]
+};
+struct GPURunState {            // getp_run.cpp:84-176
+  void *x;                      // bf16 [batch, hidden_dim], the residual stream
+  void *t;                      // bf16 [batch, hidden_dim], normalised rows (not written here: the library keeps its own)
+};
+struct GPUTransformer {         // getp_run.cpp:206-212
+  Config config;
+  GPUTransformerWeights weights;
+  GPURunState state;
+};
+inline TPGroup *tp_groups() {   // getp_run.cpp:216
+  static TPGroup g[MAX_GPUS];
+  return g;
+}
+
+// moe_gpu_120b / moe_gpu (getp_run.cpp:2896, :2540) with the reference's signature and contract: reads the rows
+// state.x[row_offset .. row_offset + batch_size) of the residual stream and weights.rms_ffn_w of the layer, and
+// adds the MoE output into state.x in place; called by the host thread of the current device, concurrently by
+// the threads of a TP group.  The per-device handle and group are found through moe_b200_handles() and
+// tp_groups(), indexed by the current device as the reference indexes gpu_transformers[] and tp_groups[].
+inline void moe_gpu_120b(GPUTransformer *gpu_t, int layer_idx, int batch_size, int row_offset, cudaStream_t sMoe) {
+  if (batch_size <= 0) return;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) moe_b200_die(nullptr, "moe_gpu_120b: cudaGetDevice", MOE_ERR_CUDA);
+  const size_t H = static_cast<size_t>(gpu_t->config.hidden_dim);
+  char *x = static_cast<char *>(gpu_t->state.x) + static_cast<size_t>(row_offset) * H * 2;
+  const char *gain = static_cast<const char *>(gpu_t->weights.rms_ffn_w) + static_cast<size_t>(layer_idx) * H * 2;
+  moe_gpu_b200_block(tp_groups()[dev], layer_idx, x, gain, batch_size, sMoe);
+}
+inline void moe_gpu(GPUTransformer *gpu_t, int layer_idx, int batch_size, int row_offset, cudaStream_t sMoe) {
+  moe_gpu_120b(gpu_t, layer_idx, batch_size, row_offset, sMoe);   // one code path serves both model sizes
+}
+#endif  // MOE_B200_SHIM_NO_TYPES

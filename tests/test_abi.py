@@ -84,16 +84,33 @@ def test_cpp_shim_compiles_and_links(tmp_path):
     import shutil
     import subprocess
     src = tmp_path / "shim.cpp"
-    src.write_text('#include "moe_b200_shim.hpp"\n'
-                   'int main() { TPGroup tp; tp_init(tp, 8, 5, 4); int s, n; mlp1_shard(5760, 4, 1, s, n);\n'
-                   '  int a, b; mlp2_shard_input(2880, 4, 3, a, b);\n'
-                   '  return (tp.group_id == 1 && tp.rank_in_group == 1 && tp.group_devs[3] == 7 && s == 1440 && n == 1440\n'
-                   '          && a == 2160 && b == 720) ? 0 : 1; }\n')
+    src.write_text(r"""
+#include <thread>
+#include "moe_b200_shim.hpp"
+// every name of the reference's MoE boundary must exist with the reference's parameter lists
+static void (*p_moe_gpu)(GPUTransformer *, int, int, int, cudaStream_t) = &moe_gpu;
+static void (*p_moe_gpu_120b)(GPUTransformer *, int, int, int, cudaStream_t) = &moe_gpu_120b;
+static void (*p_allgather)(void *, const void *, int, int, void *const[], const TPGroup &, cudaStream_t) = &ring_allgather_rows_bf16;
+static void (*p_allreduce)(void *, void *const[], size_t, void *, const TPGroup &, cudaStream_t) = &ring_allreduce_sum_bf16;
+int main() {
+  TPGroup tp; tp_init(tp, 8, 5, 4); int s, n; mlp1_shard(5760, 4, 1, s, n);
+  int a, b; mlp2_shard_input(2880, 4, 3, a, b);
+  GPUTransformer gt = {}; gt.config.hidden_dim = 2880; gt.state.x = nullptr; gt.weights.rms_ffn_w = nullptr;
+  // tp_group_barrier: four host threads of one group meet three times
+  TPGroup g[4]; int order = 0;
+  for (int r = 0; r < 4; ++r) tp_init(g[r], 4, r, 4);
+  std::thread th[4];
+  for (int r = 0; r < 4; ++r) th[r] = std::thread([&, r] { for (int i = 0; i < 3; ++i) { tp_group_barrier(g[r]); __sync_fetch_and_add(&order, 1); tp_group_barrier(g[r]); } });
+  for (auto &t : th) t.join();
+  return (tp.group_id == 1 && tp.rank_in_group == 1 && tp.group_devs[3] == 7 && s == 1440 && n == 1440
+          && a == 2160 && b == 720 && order == 12 && p_moe_gpu && p_moe_gpu_120b && p_allgather && p_allreduce) ? 0 : 1; }
+""")
     gxx = shutil.which("g++")
     if gxx is None or not os.path.exists("/usr/local/cuda/include/cuda_runtime.h"):
         pytest.skip("no host compiler or CUDA headers")
     exe = tmp_path / "shim"
     libdir = os.path.join(ROOT, "gpt-oss_b200")
-    subprocess.run([gxx, "-std=c++17", "-I" + os.path.join(ROOT, "include"), "-I/usr/local/cuda/include", str(src),
-                    "-L" + libdir, "-lmoe_b200", "-Wl,-rpath," + libdir, "-o", str(exe)], check=True)
+    subprocess.run([gxx, "-std=c++17", "-pthread", "-I" + os.path.join(ROOT, "include"), "-I/usr/local/cuda/include", str(src),
+                    "-L" + libdir, "-lmoe_b200", "-L/usr/local/cuda/lib64", "-lcudart", "-Wl,-rpath," + libdir,
+                    "-Wl,-rpath,/usr/local/cuda/lib64", "-o", str(exe)], check=True)
     assert subprocess.run([str(exe)]).returncode == 0

@@ -119,6 +119,12 @@ def test_tp_forward_single_rank_group(pkg, synth, port):
         blk.synchronize()
         assert np.array_equal(d_rs.cpu().numpy(), d_plain.cpu().numpy())
         assert np.array_equal(blk.debug(pkg.DBG_TP_PARTIAL).view(np.int16), d_plain.cpu().numpy())
+        # all-reduce over a group of one leaves the values as they are
+        d_ar = d_plain.clone()
+        blk.tp_allreduce(d_ar.data_ptr(), T * H - (T * H) % 8, torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        blk.synchronize()
+        assert np.array_equal(d_ar.cpu().numpy(), d_plain.cpu().numpy())
     finally:
         blk.close()
 

@@ -85,6 +85,22 @@ def main():
         e = np.abs(pkg.synth.bf16_bits_to_f32(d_rss[it].cpu().numpy().view(np.uint16)).astype(np.float64) - ref_rows)
         r_rms = max(1.0, float(np.sqrt((ref_rows ** 2).mean())))
         assert e.mean() / np.abs(ref_rows).mean() <= 5e-3 and e.max() <= 2e-2 * r_rms, (it, e.mean(), e.max(), r_rms)
+    # all-reduce (ring_allreduce_sum_bf16, tp_ring.hpp:253-331): every rank ends with the rank-ordered fp32 sum
+    rng = np.random.default_rng(100 + rank)
+    n_el = rows_local * world * H
+    for it in range(3):
+        mine_f = rng.normal(0, 1, size=n_el).astype(np.float32)
+        mine_b = pkg.synth.f32_to_bf16_bits(mine_f)
+        d_buf = torch.from_numpy(mine_b.view(np.int16).copy()).cuda()
+        blk.tp_allreduce(d_buf.data_ptr(), n_el, stream)
+        torch.cuda.synchronize()
+        blk.synchronize()
+        allb = [torch.empty(n_el, dtype=torch.int16) for _ in range(world)]
+        dist.all_gather(allb, torch.from_numpy(mine_b.view(np.int16).copy()))
+        acc = np.zeros(n_el, dtype=np.float32)
+        for r in range(world):
+            acc = acc + pkg.synth.bf16_bits_to_f32(allb[r].numpy().view(np.uint16))
+        assert np.array_equal(d_buf.cpu().numpy().view(np.uint16), pkg.synth.f32_to_bf16_bits(acc)), f"all-reduce round {it}"
     # the reference's calling form over the group: x <- x + MoE(rmsnorm(x) * gain) on each rank's rows
     x_bits, gain_bits = pkg.synth.make_residual(rows_local * world, H, seed=9)
     xf, gf = pkg.synth.bf16_bits_to_f32(x_bits), pkg.synth.bf16_bits_to_f32(gain_bits)
