@@ -18,7 +18,7 @@ __device__ __forceinline__ int expert_of_row(const int *offsets, int E, int r) {
   return lo;
 }
 
-// dot of one weight row (packed codes inside the weight tiles: `codes` points at the row's 64 bytes in the
+// dot of one weight row (packed codes inside the 16 KB weight tiles: `codes` points at the row's 64 bytes in the
 // first tile of its row block, the next 128 k follow one tile further; raw row-major scales) with an fp16 row
 __device__ __forceinline__ float warp_dot_mxfp4(const uint8_t *codes, const uint8_t *scales, const __half *x,
                                                 int K, int lane) {

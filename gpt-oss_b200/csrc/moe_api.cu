@@ -54,9 +54,9 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// Weight tiles (LayerWeights::w1_tiles): every 13 KB tile starts with 192 rows x 64 bytes of packed e2m1 codes,
+// Weight tiles (LayerWeights::w1_tiles): every 16 KB tile starts with 240 rows x 64 bytes of packed e2m1 codes,
 // declared to TMA as 4-bit elements that it expands to the 8-bit containers of the block-scaled MMA
-// (16U4_ALIGN16B): dims {128 codes, 192 rows, tiles}, one box = the codes of one tile, a contiguous 12 KB read.
+// (16U4_ALIGN16B): dims {128 codes, 240 rows, tiles}, one box = the codes of one tile, a contiguous 15 KB read.
 int make_weight_map(moe_ctx *c, CUtensorMap *m, const uint8_t *base, size_t n_tiles) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(c, MOE_ERR_CUDA, "cuTensorMapEncodeTiled not available");
@@ -68,6 +68,25 @@ int make_weight_map(moe_ctx *c, CUtensorMap *m, const uint8_t *base, size_t n_ti
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(c, MOE_ERR_CUDA, "cuTensorMapEncodeTiled(weights, %zu tiles) -> %d", n_tiles, (int)r);
+  return MOE_OK;
+}
+
+// e4m3 activation tiles: [token tile][k slice][128 rows][128 bytes], so that the 16 KB a work item needs for one
+// k slice are one contiguous run (rows of K bytes would make the box 128 separate 128-byte pieces).  To TMA
+// this is a matrix of 128-byte rows; box = 128 x 128, 128-byte swizzle.
+int make_act_map(moe_ctx *c, CUtensorMap *m, const uint8_t *base, size_t n_tiles, int n_kc) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(c, MOE_ERR_CUDA, "cuTensorMapEncodeTiled not available");
+  const cuuint64_t rows = static_cast<cuuint64_t>(n_tiles) * n_kc * kTileM;
+  const cuuint64_t dims[2] = {kChunkK, rows};
+  const cuuint64_t strides[1] = {kChunkK};
+  const cuuint32_t box[2] = {kChunkK, kTileM};
+  const cuuint32_t es[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t *>(base), dims, strides, box, es,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(c, MOE_ERR_CUDA, "cuTensorMapEncodeTiled(activations, %zu tiles x %d slices) -> %d", n_tiles, n_kc, (int)r);
   return MOE_OK;
 }
 
@@ -90,9 +109,9 @@ int dev_alloc(moe_ctx *c, T **p, size_t n) {
   return MOE_OK;
 }
 
-// One weight matrix -> the tiles the GEMM streams (LayerWeights::w1_tiles).  codes: [E][R] rows of
+// One weight matrix -> the 16 KB tiles the GEMM streams (LayerWeights::w1_tiles).  codes: [E][R] rows of
 // row_bytes packed bytes at `pitch`; raw: E8M0 scales [E][R][nblk].  In a tile the scale of row r (of the tile's
-// 192), k block kb sits at byte (r%32)*16 + (r/32 %4)*4 + kb of atom r/128, the order tcgen05.cp puts them into
+// 240), k block kb sits at byte (r%32)*16 + (r/32 %4)*4 + kb of atom r/128, the order tcgen05.cp puts them into
 // tensor memory; 127 (scale 1) and zero codes where no row or no block exists.
 void tile_weights(const uint8_t *codes, size_t pitch, size_t row_bytes, const uint8_t *raw, int E, int R, int nblk,
                   int n_ntiles, int n_kc, std::vector<uint8_t> &out) {
@@ -197,18 +216,18 @@ int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_b
     GemmArgs a{};
     a.work = c->work1; a.n_work = c->n_work; a.K = H; a.R = c->R1;
     a.n_kchunks = (H + kChunkK - 1) / kChunkK; a.n_ntiles = n_nt1;
-    a.w_tiles = w.w1_tiles; a.act = c->xq; a.sfa = c->sfa_x; a.sfa_tile_stride = kSfAtomBytes; a.bias = w.b1; a.add_bias = 1;
+    a.w_tiles = w.w1_tiles; a.sfa = c->sfa_x; a.sfa_tile_stride = kSfAtomBytes; a.bias = w.b1; a.add_bias = 1;
     a.hq_out = c->hq; a.hq_joff = c->joff; a.hq_nkc = (c->Kw + kChunkK - 1) / kChunkK; a.y_out = nullptr; a.ld_out = c->Kw;
     a.h_exp = c->h_exp;
     a.limit = c->cfg.swiglu_limit; a.alpha = c->cfg.swiglu_alpha; a.status = status;
-    launch_expert_gemm_mlp1(w.tm_w1, a, c->sm_count, s);
+    launch_expert_gemm_mlp1(w.tm_w1, c->tm_x1, a, c->sm_count, s);
     mark();
     GemmArgs b = a;
     b.work = c->work2; b.n_work = c->n_work + 1; b.K = c->Kw; b.R = H;
     b.n_kchunks = (c->Kw + kChunkK - 1) / kChunkK; b.n_ntiles = n_nt2;
-    b.w_tiles = w.w2_tiles; b.act = c->hq; b.sfa = c->sfa_h; b.sfa_tile_stride = 0; b.bias = w.b2; b.add_bias = add_b2;
+    b.w_tiles = w.w2_tiles; b.sfa = c->sfa_h; b.sfa_tile_stride = 0; b.bias = w.b2; b.add_bias = add_b2;
     b.hq_out = nullptr; b.y_out = c->ybuf; b.ld_out = H;
-    launch_expert_gemm_mlp2(w.tm_w2, b, c->sm_count, s);
+    launch_expert_gemm_mlp2(w.tm_w2, c->tm_x2, b, c->sm_count, s);
   }
   mark();
   if (!tpcall) {
@@ -379,6 +398,8 @@ int moe_create(const moe_config *cfg, moe_handle *out) {
   // Rows past the current batch are read (and discarded) by token tiles that overhang; keep them finite.
   CU_TRY(c, cudaMemset(c->xperm, 0, P * c->H * sizeof(__half)));
   CU_TRY(c, cudaMemset(c->hbuf, 0, P * c->Kw * sizeof(__half)));
+  if ((rc = make_act_map(c, &c->tm_x1, c->xq, c->max_tiles, n_kc1))) return rc;
+  if ((rc = make_act_map(c, &c->tm_x2, c->hq, c->max_tiles, n_kc2))) return rc;
   return MOE_OK;
 }
 

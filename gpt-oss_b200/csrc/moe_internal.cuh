@@ -15,19 +15,16 @@
 namespace moe {
 
 // ---- tiling constants of the expert GEMM (expert_gemm_sm100.cu) -------------
-constexpr int kTileN = 160;        // weight rows per work item (UMMA N); divides 5760, 2880 and 1440
+constexpr int kTileN = 240;        // weight rows per work item (UMMA N); divides 5760 and 2880
 constexpr int kTileNPad = 256;     // rows reserved per weight tile in shared memory / scale atoms
 constexpr int kChunkK = 128;       // reduction elements per shared-memory stage (4 MMA k-steps of 32)
 constexpr int kTokTile = 64;       // token rows per work item
 constexpr int kTileM = 2 * kTokTile;  // UMMA M: each token contributes a high and a low e4m3 row
 constexpr int kSfAtomBytes = 512;  // scale factors of 128 rows x 4 k-blocks, tensor-memory order
-constexpr int kSfbChunkBytes = 2 * kSfAtomBytes;  // weight scales of one tile (192 rows in two atoms)
-constexpr int kWTileCodes = kTileN * kChunkK / 2;  // 10240 bytes of packed codes per weight tile
-constexpr int kWTileStride = kWTileCodes + kSfbChunkBytes;  // 11264: codes, then scales
-static_assert(kWTileStride % 32 == 0, "tile stride: a TMA stride of packed 4-bit data is a multiple of 32 bytes");
-// Quantised activations: per (token tile, k slice) 16 KB as [16-byte column c = 0..7][128 rows][16 bytes], so
-// that the 32 rows a loader warp reads for one column are 512 contiguous bytes.
-constexpr int kActColBytes = kTileM * 16;
+constexpr int kSfbChunkBytes = 2 * kSfAtomBytes;  // weight scales of one tile (240 rows in two atoms)
+constexpr int kWTileCodes = kTileN * kChunkK / 2;  // 15360 bytes of packed codes per weight tile
+constexpr int kWTileStride = kWTileCodes + kSfbChunkBytes;  // 16384: codes, then scales
+static_assert(kWTileStride == 16384, "weight tiles are 16 KB");
 
 // Device status bits (MOE_DBG_STATUS).
 enum : unsigned {
@@ -90,12 +87,11 @@ struct GemmArgs {
   int n_kchunks;  // ceil(K / kChunkK)
   int n_ntiles;   // ceil(R / kTileN)
   const uint8_t *w_tiles;     // weight tiles [E][n_ntiles][n_kchunks][kWTileStride], see LayerWeights::w1_tiles
-  const uint8_t *act;         // quantised activations (xq or hq), see kActColBytes
   const uint8_t *sfa;         // activation scales, one 512-byte atom per token tile
   int sfa_tile_stride;        // bytes between token tiles' atoms (0: one atom shared by all tiles)
   const __nv_bfloat16 *bias;  // [E][R]
   int add_bias;               // MLP2 on TP ranks other than 0 leaves the bias out
-  uint8_t *hq_out;            // MLP1: quantised SwiGLU output, e4m3 tiles [tile][hq_nkc] of the layout above
+  uint8_t *hq_out;            // MLP1: quantised SwiGLU output, e4m3 tiles [tile][hq_nkc][128 rows][128 bytes]
   int hq_joff, hq_nkc;        //       column of the shard's first output inside MLP2's k window; its k slices
   __half *y_out;              // MLP2: [P, ld_out] fp16
   int ld_out;
@@ -106,8 +102,8 @@ struct GemmArgs {
 
 struct LayerWeights {
   bool loaded = false;
-  // MLP1 weights as the GEMM streams them: one 13 KB tile per (expert, 192-row block, 128-wide slice of k),
-  // tiles of a block in k order: [192 rows x 64 bytes of packed e2m1 codes][two 512-byte E8M0 scale atoms in
+  // MLP1 weights as the GEMM streams them: one 16 KB tile per (expert, 240-row block, 128-wide slice of k),
+  // tiles of a block in k order: [240 rows x 64 bytes of packed e2m1 codes][two 512-byte E8M0 scale atoms in
   // the order tcgen05.cp wants].  Rows or k beyond the matrix hold zero codes and scale 1 (byte 127).
   uint8_t *w1_tiles = nullptr;
   __nv_bfloat16 *b1 = nullptr;   // [E, R1]
@@ -149,7 +145,7 @@ struct moe_ctx {
   int *row_slot = nullptr;          // row of the token's high term in xq [max_pairs]
   __half *xperm = nullptr;          // expert_input_buffer [max_pairs, H]   fp16 (validation GEMM only)
   __half *hbuf = nullptr;           // gate_up             [max_pairs, Dl]  fp16 (validation GEMM only)
-  uint8_t *xq = nullptr;            // expert_input_buffer as e4m3 high/low rows, [max_tiles][k slices][8][128 rows][16 B]
+  uint8_t *xq = nullptr;            // expert_input_buffer as e4m3 high/low rows, [max_tiles][k slices][128 rows][128 B]
   uint8_t *hq = nullptr;            // gate_up as e4m3 high/low rows, same tiling over MLP2's k window
   uint8_t *sfa_x = nullptr;         // per-tile scale atoms of xq [max_tiles][512]
   uint8_t *sfa_h = nullptr;         // the one scale atom of hq   [512]
@@ -163,6 +159,7 @@ struct moe_ctx {
   int *n_work = nullptr;            // [2]
   int max_work1 = 0, max_work2 = 0;
   unsigned int *status = nullptr;
+  CUtensorMap tm_x1, tm_x2;
   int last_rows = 0;
   long long launches = 0;
   moe::TpPeers peers = {};          // TP group view; own entries are set at creation
@@ -211,8 +208,10 @@ void launch_rmsnorm_rows(const __nv_bfloat16 *x, const __nv_bfloat16 *w, __nv_bf
 
 // expert_gemm_sm100.cu
 cudaError_t expert_gemm_init();
-void launch_expert_gemm_mlp1(const CUtensorMap &tm_w, const GemmArgs &a, int grid, cudaStream_t s);
-void launch_expert_gemm_mlp2(const CUtensorMap &tm_w, const GemmArgs &a, int grid, cudaStream_t s);
+void launch_expert_gemm_mlp1(const CUtensorMap &tm_w, const CUtensorMap &tm_x, const GemmArgs &a, int grid,
+                             cudaStream_t s);
+void launch_expert_gemm_mlp2(const CUtensorMap &tm_w, const CUtensorMap &tm_x, const GemmArgs &a, int grid,
+                             cudaStream_t s);
 
 // tp_collectives.cu
 void launch_tp_allgather_push(const __nv_bfloat16 *src, int rows_local, int H, const TpPeers &peers, int tp, int rank,

@@ -441,9 +441,9 @@ quantize_rows_kernel(const __nv_bfloat16 *__restrict__ t, const int *__restrict_
   int e = static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu) - 127 - 7;
   e = max(-120, min(e, 120));
   const float inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);  // 2^-e
-  // activation tiles: [tile][k slice][16-byte column][128 rows][16 bytes]; 8 elements never straddle a column
+  // activation tiles: [tile][k slice][128 rows][128 bytes]; 8 elements never straddle a slice
   const int n_kc = (H + kChunkK - 1) / kChunkK;
-  uint8_t *tile_hi = xq + static_cast<size_t>(tile) * n_kc * (kTileM * kChunkK) + i2 * 16;
+  uint8_t *tile_hi = xq + (static_cast<size_t>(tile) * n_kc * kTileM + i2) * kChunkK;
 #pragma unroll
   for (int u = 0; u < kQrVec; ++u) {
     const int c = threadIdx.x + u * kQrThreads;
@@ -471,10 +471,9 @@ quantize_rows_kernel(const __nv_bfloat16 *__restrict__ t, const int *__restrict_
       const uint32_t d2 = __nv_cvt_float2_to_fp8x2(make_float2(rs[2], rs[3]), __NV_SATFINITE, __NV_E4M3);
       l8[g] = c2 | (d2 << 16);
     }
-    // slice c/16; inside it 16-byte column (c%16)/2, then the row, then byte 8*(c%2)
-    uint8_t *dst = tile_hi + static_cast<size_t>(c >> 4) * (kTileM * kChunkK) + ((c & 15) >> 1) * kActColBytes + (c & 1) * 8;
+    uint8_t *dst = tile_hi + static_cast<size_t>(c >> 4) * (kTileM * kChunkK) + (c & 15) * 8;  // slice c/16, byte 8*(c%16)
     *reinterpret_cast<uint2 *>(dst) = make_uint2(h8[0], h8[1]);
-    *reinterpret_cast<uint2 *>(dst + 16) = make_uint2(l8[0], l8[1]);                           // the low row follows
+    *reinterpret_cast<uint2 *>(dst + kChunkK) = make_uint2(l8[0], l8[1]);                      // the low row follows
   }
   if (threadIdx.x < 2) {
     const int rr = i2 + threadIdx.x;  // row inside the tile: even = high, odd = low

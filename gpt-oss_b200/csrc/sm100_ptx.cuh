@@ -76,10 +76,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 }
 
 // The same wait for a whole converged warp.  Every decision is taken by a vote, so the 32 lanes leave
-// together (success or give-up) and may go on to warp-wide instructions (elect.sync, tcgen05.st).  Roles
-// that issue tcgen05.mma or TMA keep their warp converged and elect one lane per instruction group: the
-// operands of those instructions then live in uniform registers instead of being moved there one by one
-// from the registers of a lone diverged lane.
+// together (success or give-up) and may go on to warp-wide instructions (elect.sync).  The roles that
+// issue tcgen05.mma or TMA keep their warp converged and elect one lane per instruction group: the
+// operands of those instructions (descriptors, tensor-memory addresses) are then computed once per warp in
+// uniform registers; a lone diverged lane has to move every one of them there, which on this part costs
+// the issuing thread more than the instructions themselves.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
                                                unsigned int *status, unsigned int code) {
   if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
@@ -189,41 +190,6 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16
       : "memory");
 }
 
-// One warp, 32 lanes x 32 consecutive 32-bit columns: lane i writes its 128 bytes v[0..7] (in order) into
-// columns taddr.col .. +31 of tensor-memory lane taddr.lane + i.
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint4 (&v)[8]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-      ::"r"(taddr), "r"(v[0].x), "r"(v[0].y), "r"(v[0].z), "r"(v[0].w), "r"(v[1].x), "r"(v[1].y), "r"(v[1].z),
-      "r"(v[1].w), "r"(v[2].x), "r"(v[2].y), "r"(v[2].z), "r"(v[2].w), "r"(v[3].x), "r"(v[3].y), "r"(v[3].z),
-      "r"(v[3].w), "r"(v[4].x), "r"(v[4].y), "r"(v[4].z), "r"(v[4].w), "r"(v[5].x), "r"(v[5].y), "r"(v[5].z),
-      "r"(v[5].w), "r"(v[6].x), "r"(v[6].y), "r"(v[6].z), "r"(v[6].w), "r"(v[7].x), "r"(v[7].y), "r"(v[7].z),
-      "r"(v[7].w)
-      : "memory");
-}
-
-// The same for 16 columns (64 bytes per lane).
-__device__ __forceinline__ void tmem_st16v(uint32_t taddr, const uint4 (&v)[4]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-      ::"r"(taddr), "r"(v[0].x), "r"(v[0].y), "r"(v[0].z), "r"(v[0].w), "r"(v[1].x), "r"(v[1].y), "r"(v[1].z),
-      "r"(v[1].w), "r"(v[2].x), "r"(v[2].y), "r"(v[2].z), "r"(v[2].w), "r"(v[3].x), "r"(v[3].y), "r"(v[3].z),
-      "r"(v[3].w)
-      : "memory");
-}
-
-// 16-byte read-only load that does not allocate in L1 (streamed once per work item).
-__device__ __forceinline__ uint4 ld_nc_v4(const void *p) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
-
 // ---------------------------------------------------------------- tcgen05.mma
 // D[tmem] (+)= A[tmem] * B[smem]^T, kind::f16 (fp16 operands, fp32 accumulate),
 // M = 128, K = 16 per instruction, issued by ONE thread.
@@ -276,18 +242,6 @@ __device__ __forceinline__ void mma_mxf8f6f4_ss(uint32_t d_tmem, uint64_t a_desc
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
-      : "memory");
-}
-
-// The same instruction with its A operand in tensor memory: lane = row of A, each 32-bit column four
-// consecutive bytes of k (8 columns per K = 32 instruction); B from shared memory.
-__device__ __forceinline__ void mma_mxf8f6f4_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                                uint32_t accumulate, uint32_t sfa_tmem, uint32_t sfb_tmem) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], [%1], %2, %3, [%5], [%6], p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
       : "memory");
 }
 
