@@ -186,10 +186,12 @@ def cpu_reference_arm(layer, tokens_bits, steps: int, warmup: int):
     return steps * n / dt, kind, cores, dt / steps * 1e3, last
 
 
-def parity_figures(synth, got_bits, ref_out, got_idx, ref_idx, ref_logits, got_f32=None) -> dict:
+def parity_figures(synth, got_bits, ref_out, got_idx, ref_idx, ref_logits, got_f32=None, tp: int = 1) -> dict:
     """Raw error figures of `got_bits` (bf16 bit patterns) against the oracle's float output for the same rows.
     Rows whose expert selection differs from the oracle's are counted and left out of the output figures
-    (allowed only where the oracle's own logits are within 1e-5 at the place that differs)."""
+    (allowed only where the oracle's own logits are within 1e-5 at the place that differs).  In a TP group
+    every rank's partial travels as bf16 and the sum is rounded once more (as in the reference,
+    getp_run.cpp:3206-3246): the max-abs bound grows by half a bf16 ulp of the largest output per rounding."""
     same = (got_idx == ref_idx).all(axis=1)
     k = ref_idx.shape[1]
     srt = np.sort(ref_logits, axis=1)[:, ::-1]
@@ -199,13 +201,16 @@ def parity_figures(synth, got_bits, ref_out, got_idx, ref_idx, ref_logits, got_f
     err = np.abs(got - ref)
     rms = float(np.sqrt((ref ** 2).mean()))
     floor = np.abs(synth.bf16_bits_to_f32(synth.f32_to_bf16_bits(ref.astype(np.float32))).astype(np.float64) - ref)
+    max_bound = 2e-2 * max(1.0, rms) + ((tp + 1) * 2.0 ** -9 * float(np.abs(ref).max()) if tp > 1 else 0.0)
     out = {"rows": int(len(same)), "selection_mismatches": int((~same).sum()),
            "selection_mismatches_with_clear_gap": int((~same & ~near_tie).sum()),
            "max_abs": float(err.max()), "rms_ref": rms, "max_abs_over_rms": float(err.max() / rms),
            "mean_rel": float(err.mean() / np.abs(ref).mean()),
            "max_abs_of_bf16_rounding_alone": float(floor.max()),
-           "bounds": "mean_rel <= 5e-3; max_abs <= 2e-2 * max(1, rms_ref)",
-           "within_bounds": bool(err.mean() / np.abs(ref).mean() <= 5e-3 and err.max() <= 2e-2 * max(1.0, rms)
+           "bounds": "mean_rel <= 5e-3; max_abs <= 2e-2 * max(1, rms_ref)"
+                     + (f" + {tp + 1} x 2^-9 x max|ref| (bf16 partials of {tp} ranks and their rounded sum)" if tp > 1 else ""),
+           "max_abs_bound": max_bound,
+           "within_bounds": bool(err.mean() / np.abs(ref).mean() <= 5e-3 and err.max() <= max_bound
                                  and not (~same & ~near_tie).any())}
     if got_f32 is not None:
         e32 = np.abs(got_f32.astype(np.float64)[same] - ref)
@@ -248,9 +253,26 @@ def case_tokens(args, shape):
         ms = e0.elapsed_time(e1) / args.steps
         counts = blk.debug(pkg.DBG_COUNTS)
         active = int((counts > 0).sum())
+        # the same call captured once in a CUDA graph and replayed (the call is stream-ordered work only): what a
+        # caller pays per layer when it does not launch the kernels one by one from the host
+        side = torch.cuda.Stream()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            blk.forward(0, d_t.data_ptr(), T, d_o.data_ptr(), 0, torch.cuda.current_stream().cuda_stream)
+        for _ in range(3):
+            g.replay()
+        torch.cuda.synchronize()
+        e0.record(stream)
+        for _ in range(args.steps):
+            g.replay()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        blk.synchronize()
+        ms_graph = e0.elapsed_time(e1) / args.steps
         flops, nbytes = synth.algorithmic_work(T, H, D, E, K, active)
         roof_ms = max(nbytes / hbm / 1e6, flops / tc / 1e9)
         print(json.dumps({"case": "tokens", "shape": shape["name"], "zipf": args.zipf, "rows": T, "ms_per_block": ms,
+                          "ms_per_block_cuda_graph": ms_graph,
                           "tokens_per_s": T / ms * 1e3, "active_experts": active,
                           "max_rows_per_expert": int(counts.max()), "roofline_ms": roof_ms,
                           "frac_of_roofline": roof_ms / ms}), flush=True)
@@ -509,11 +531,33 @@ def main():
     e2e_s = max_over_ranks(time.perf_counter() - t0)
     barrier()
 
+    # ---- C2: the copies of those steps alone (no block), all ranks at once: what host<->device traffic allows ----
+    c_in, c_out = torch.cuda.Stream(), torch.cuda.Stream()
+    pin_t = [torch.from_numpy(b.array.view(np.int16)) for b in pin_in]       # views of the pinned buffers
+    pout_t = [torch.from_numpy(b.array.view(np.int16)) for b in pin_out]
+    n_copy = min(args.steps, 50)
+
+    def copy_steps(n):
+        for i in range(n):
+            with torch.cuda.stream(c_in):
+                d_t.copy_(pin_t[i % n_pin], non_blocking=True)
+            with torch.cuda.stream(c_out):
+                pout_t[i % n_pin].copy_(d_o, non_blocking=True)
+        c_in.synchronize(); c_out.synchronize()
+
+    saved_out = pin_out[(args.steps - 1) % n_pin].array[:min(PARITY_ROWS, T)].copy()   # the last step's rows, before the probe overwrites them
+    copy_steps(3)
+    barrier(); torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    copy_steps(n_copy)
+    copy_s = max_over_ranks(time.perf_counter() - t0)
+    barrier()
+
     # ---- parity: rank 0's first rows, as they came back through the host call, against the CPU oracle ----
     parity = None
     if rank == 0:
         nrow = min(PARITY_ROWS, T)
-        got_bits = pin_out[(args.steps - 1) % n_pin].array[:nrow].copy()
+        got_bits = saved_out[:nrow]
         got_idx = blk.debug(pkg.DBG_TOPK_IDX)[:nrow]        # rank 0's rows are the first rows of the union
         port = _oracle().Port()
         port.set_threads(_oracle().host_cores())
@@ -523,7 +567,7 @@ def main():
             blk.forward(0, d_t.data_ptr(), T, 0, pkg.FWD_PARTIAL_F32, sp)
             torch.cuda.synchronize()
             got_f32 = blk.debug(pkg.DBG_OUT_F32)[:nrow]
-        parity = parity_figures(synth, got_bits, ref_out, got_idx, ref_idx, ref_logits, got_f32)
+        parity = parity_figures(synth, got_bits, ref_out, got_idx, ref_idx, ref_logits, got_f32, tp)
         parity["against"] = "C restatement of run.cpp:657-748 (pinned bit-exact to the reference's forward())"
 
     # ---- D (TP only): the two collectives alone, this library's peer-memory kernels vs NCCL ----
@@ -556,7 +600,7 @@ def main():
                 "allgather_gbs_per_direction": {"ours": per_dir / ours_ag / 1e6, "nccl": per_dir / nccl_ag / 1e6},
                 "reduce_scatter_gbs_per_direction": {"ours": per_dir / ours_rs / 1e6, "nccl": per_dir / nccl_rs / 1e6},
                 "nvlink_peer_copy_measured_gbs": 770.0}
-    loss_like = float(synth.bf16_bits_to_f32(pin_out[(args.steps - 1) % n_pin].array[:4]).sum())  # the result was read back
+    loss_like = float(synth.bf16_bits_to_f32(saved_out[:4]).sum())  # the result was read back
     clocks = sampler.stop() if sampler else None
 
     if rank != 0:
@@ -586,7 +630,10 @@ def main():
                 "d2h_bytes_per_step": T * H * 2, "ms_per_step": e2e_s / args.steps * 1e3,
                 "api": "moe_forward_host_submit/_wait, 3 batches in flight, pinned buffers",
                 "host_cpu_us_per_step": {"submit": host_cpu["submit_s"] / args.steps * 1e6,
-                                         "wait": host_cpu["wait_s"] / args.steps * 1e6}},
+                                         "wait": host_cpu["wait_s"] / args.steps * 1e6},
+                "copies_alone_ms_per_step": copy_s / n_copy * 1e3,
+                "copies_alone_note": "the same host->device and device->host copies on two streams with no block in "
+                                     "between, all ranks at once: the floor that host memory and PCIe set for a step"},
         "gpu_launches": gpu_launches,
         "clocks": clocks,
         "roofline": {"kernel": "expert_gemm_kernel<1> (MLP1 grouped GEMM + SwiGLU)", "bound": "hbm",
@@ -619,7 +666,7 @@ def main():
         r_logits, r_idx, _, r_out = ref_last
         n = CPU_SAMPLE_TOKENS
         out["parity"]["against_timed_cpu_run"] = dict(
-            parity_figures(synth, pin_out[(args.steps - 1) % n_pin].array[:n], r_out,
+            parity_figures(synth, saved_out[:n], r_out,
                            blk.debug(pkg.DBG_TOPK_IDX)[:n], r_idx, r_logits), kind=kind)
     print(json.dumps(out))
     for b in pin_in + pin_out:

@@ -152,7 +152,7 @@ namespace moe {
 
 int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_bfloat16 *out_dev, unsigned flags,
                  cudaStream_t s, const __nv_bfloat16 *t_local, int tp_rows_local, const __nv_bfloat16 *residual,
-                 unsigned int *status) {
+                 unsigned int *status, const __nv_bfloat16 *norm_gain) {
   if (status == nullptr) status = c->status;
   if (layer < 0 || layer >= c->L || !t || rows <= 0 || rows > c->max_rows)
     return fail(c, MOE_ERR_INVALID, "moe_forward: layer %d rows %d (max %d)", layer, rows, c->max_rows);
@@ -175,6 +175,11 @@ int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_b
     c->prof_events.push_back(ev);
   };
   mark();
+  if (norm_gain != nullptr && !tpcall) {   // step 0 of moe_gpu on one GPU: t = rmsnorm(x) * gain
+    launch_rmsnorm_rows(residual, norm_gain, c->t_norm, rows, H, s);
+    t = c->t_norm;
+    c->launches += 1;
+  }
   if (!tpcall) {
     const int splits = router_splits(T, H, c->sm_count);
     launch_router_partials(t, w.router_w3, c->router_part, T, H, E, splits, s);
@@ -186,7 +191,16 @@ int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_b
     ++c->tp_epoch;
     CU_TRY(c, cudaEventRecord(c->ev_fork, s));
     CU_TRY(c, cudaStreamWaitEvent(c->aux_stream, c->ev_fork, 0));
-    launch_tp_allgather_push(t_local, tp_rows_local, H, c->peers, tp, rank, c->sm_count, c->aux_stream);
+    if (norm_gain != nullptr) {
+      // moe_block: the push normalises the residual rows on the fly (side stream) while this stream
+      // normalises the same rows into t_norm for the router
+      launch_tp_rmsnorm_push(residual, norm_gain, tp_rows_local, H, c->peers, tp, rank, c->aux_stream);
+      launch_rmsnorm_rows(residual, norm_gain, c->t_norm, tp_rows_local, H, s);
+      t_local = c->t_norm;
+      c->launches += 1;
+    } else {
+      launch_tp_allgather_push(t_local, tp_rows_local, H, c->peers, tp, rank, c->sm_count, c->aux_stream);
+    }
     CU_TRY(c, cudaEventRecord(c->ev_join, c->aux_stream));
     const int splits = router_splits(tp_rows_local, H, c->sm_count);
     launch_router_partials(t_local, w.router_w3, c->router_part, tp_rows_local, H, E, splits, s);

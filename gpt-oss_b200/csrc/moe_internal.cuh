@@ -216,6 +216,8 @@ void launch_expert_gemm_mlp2(const CUtensorMap &tm_w, const CUtensorMap &tm_x, c
 // tp_collectives.cu
 void launch_tp_allgather_push(const __nv_bfloat16 *src, int rows_local, int H, const TpPeers &peers, int tp, int rank,
                               int sm_count, cudaStream_t s);
+void launch_tp_rmsnorm_push(const __nv_bfloat16 *x, const __nv_bfloat16 *w, int rows_local, int H, const TpPeers &peers,
+                            int tp, int rank, cudaStream_t s);
 void launch_tp_signal_wait(const TpPeers &peers, uint32_t *my_flags, int tp, int rank, int phase, uint32_t epoch,
                            unsigned int *status, cudaStream_t s);
 void launch_tp_sum_slots(const __nv_bfloat16 *landing, int tp, int rows_local, int H, __nv_bfloat16 *out, int sm_count,
@@ -238,8 +240,12 @@ int check_tp_call(moe_ctx *c, int rows_local, const char *who);
 // moe_api.cu: the block itself.  With tp_rows_local > 0 this is a call of a tensor-parallel group: t is the
 // gather buffer, t_local this rank's rows; routing is computed for the local rows only and exchanged, the
 // combine pushes each row's partial to the rank that owns it, and out_dev receives this rank's summed rows.
+// With norm_gain set (moe_block) `residual` holds the rows of the residual stream and the call starts with
+// their RMSNorm: into c->t_norm, which then replaces t (one GPU) or t_local (TP group; the all-gather push
+// normalises on the fly).
 int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int T, __nv_bfloat16 *out_dev, unsigned flags,
                  cudaStream_t s, const __nv_bfloat16 *t_local, int tp_rows_local,
-                 const __nv_bfloat16 *residual = nullptr, unsigned int *status = nullptr);
+                 const __nv_bfloat16 *residual = nullptr, unsigned int *status = nullptr,
+                 const __nv_bfloat16 *norm_gain = nullptr);
 
 }  // namespace moe

@@ -182,14 +182,14 @@ int moe_block(moe_handle c, int layer, void *x_dev, const void *rms_w_dev, int r
   const int tp = c->cfg.tp_size;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   __nv_bfloat16 *x = static_cast<__nv_bfloat16 *>(x_dev);
-  // step 0: t = rmsnorm(x) * w; the last kernel of the block adds its result to x in place
-  launch_rmsnorm_rows(x, static_cast<const __nv_bfloat16 *>(rms_w_dev), c->t_norm, rows_local, c->H, s);
-  c->launches += 1;
+  // step 0 (t = rmsnorm(x) * w) runs inside: on one GPU as a kernel of its own, in a TP group inside the
+  // all-gather push; the last kernel of the block adds its result to x in place
   flags &= ~MOE_FWD_PARTIAL_F32;
+  const __nv_bfloat16 *gain = static_cast<const __nv_bfloat16 *>(rms_w_dev);
   if (tp > 1)
     return forward_impl(c, layer, static_cast<const __nv_bfloat16 *>(c->peers.gather[c->cfg.tp_rank]), rows_local * tp, x,
-                        flags, s, c->t_norm, rows_local, x);
-  return forward_impl(c, layer, c->t_norm, rows_local, x, flags, s, nullptr, 0, x);
+                        flags, s, x, rows_local, x, nullptr, gain);
+  return forward_impl(c, layer, x, rows_local, x, flags, s, nullptr, 0, x, nullptr, gain);
 }
 
 int moe_tp_forward_host(moe_handle c, int layer, const void *t_local_host, int rows_local, void *out_local_host,

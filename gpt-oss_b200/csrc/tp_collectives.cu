@@ -39,6 +39,53 @@ tp_allgather_push_kernel(const uint4 *__restrict__ src, size_t n_vec, TpPeers pe
   }
 }
 
+// The same push with the pre-MoE RMSNorm inside (moe_block of a TP group): block per row of the residual
+// stream; t = w * (x / sqrt(mean(x^2) + 1e-5)) with the arithmetic of rmsnorm_rows_kernel (sum of squares in
+// double, products in float, one bf16 rounding), so every rank's copy of a row equals the owner's own t bit
+// for bit; the row goes straight into slot `rank` of every peer's gather buffer.  The normalised rows are
+// never written and re-read locally for the exchange, and the push does not wait for the owner's own
+// normalisation kernel (rmsnorm_kernel_bf16_io, kernels/rmsnorm.hpp:115-164, then ring_allgather_rows_bf16).
+__global__ void __launch_bounds__(256)
+tp_rmsnorm_push_kernel(const __nv_bfloat16 *__restrict__ x, const __nv_bfloat16 *__restrict__ w, int H, TpPeers peers,
+                       int tp, size_t slot_row) {
+  __shared__ double s_part[8];
+  const uint4 *src = reinterpret_cast<const uint4 *>(x + static_cast<size_t>(blockIdx.x) * H);
+  double ss = 0.0;
+  for (int c = threadIdx.x; c < H / 8; c += blockDim.x) {
+    const uint4 v = __ldg(src + c);
+    const uint32_t in[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float a = __uint_as_float(in[j] << 16), b = __uint_as_float(in[j] & 0xffff0000u);
+      ss += static_cast<double>(a) * a + static_cast<double>(b) * b;
+    }
+  }
+#pragma unroll
+  for (int off = 16; off; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  double tot = 0.0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tot += s_part[i];
+  const float inv = static_cast<float>(1.0 / sqrt(tot / H + 1e-5));
+  const uint4 *wv = reinterpret_cast<const uint4 *>(w);
+  const size_t row_vec = (slot_row + blockIdx.x) * static_cast<size_t>(H / 8);
+  for (int c = threadIdx.x; c < H / 8; c += blockDim.x) {
+    const uint4 v = __ldg(src + c), g = __ldg(wv + c);
+    const uint32_t in[4] = {v.x, v.y, v.z, v.w}, gn[4] = {g.x, g.y, g.z, g.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float a = __uint_as_float(gn[j] << 16) * (inv * __uint_as_float(in[j] << 16));
+      const float b = __uint_as_float(gn[j] & 0xffff0000u) * (inv * __uint_as_float(in[j] & 0xffff0000u));
+      const __nv_bfloat162 q = __floats2bfloat162_rn(a, b);
+      o[j] = *reinterpret_cast<const uint32_t *>(&q);
+    }
+    const uint4 out = make_uint4(o[0], o[1], o[2], o[3]);
+    for (int r = 0; r < tp; ++r) reinterpret_cast<uint4 *>(peers.gather[r])[row_vec + c] = out;
+  }
+}
+
 // Tells every peer "my data of this phase and epoch is in place" and waits until every peer has said
 // the same.  flags layout on each rank: [phase][tp] words, word [phase][r] written by rank r.
 // One warp; lane r handles peer r.  The wait is bounded (about a second).
@@ -141,6 +188,11 @@ void launch_tp_allgather_push(const __nv_bfloat16 *src, int rows_local, int H, c
   const int blocks = static_cast<int>(std::min<size_t>((n_vec + 255) / 256, static_cast<size_t>(sm_count) * 4));
   tp_allgather_push_kernel<<<std::max(blocks, 1), 256, 0, s>>>(reinterpret_cast<const uint4 *>(src), n_vec, peers, tp,
                                                               static_cast<size_t>(rank) * n_vec);
+}
+
+void launch_tp_rmsnorm_push(const __nv_bfloat16 *x, const __nv_bfloat16 *w, int rows_local, int H, const TpPeers &peers,
+                            int tp, int rank, cudaStream_t s) {
+  tp_rmsnorm_push_kernel<<<rows_local, 256, 0, s>>>(x, w, H, peers, tp, static_cast<size_t>(rank) * rows_local);
 }
 
 void launch_tp_signal_wait(const TpPeers &peers, uint32_t *my_flags, int tp, int rank, int phase, uint32_t epoch,

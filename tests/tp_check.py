@@ -71,12 +71,12 @@ def main():
     blk.synchronize()
     blk.rows = rows_local * world
     assert np.array_equal(blk.debug(pkg.DBG_GATHER), unions[-1]), "gathered rows differ from the union"
-    my_partial = torch.from_numpy(blk.debug(pkg.DBG_TP_PARTIAL).view(np.int16).copy())
+    my_partial = torch.from_numpy(blk.debug(pkg.DBG_TP_PARTIAL).view(np.uint8).copy())    # gloo carries bytes
     parts = [torch.empty_like(my_partial) for _ in range(world)]
     dist.all_gather(parts, my_partial)
     acc = np.zeros((rows_local, H), dtype=np.float32)
     for r in range(world):                    # fp32 adds in rank order, as the kernel does
-        acc = acc + pkg.synth.bf16_bits_to_f32(parts[r].numpy().view(np.uint16)[sl_mine])
+        acc = acc + pkg.synth.bf16_bits_to_f32(parts[r].numpy().view(np.uint16).reshape(-1, H)[sl_mine])
     assert np.array_equal(d_rss[-1].cpu().numpy().view(np.uint16), pkg.synth.f32_to_bf16_bits(acc)), \
         "reduce-scatter is not the rank-ordered fp32 sum of the ranks' bf16 partials"
     for it in range(4):
@@ -84,7 +84,10 @@ def main():
         ref_rows = ref_it[sl_mine].astype(np.float64)
         e = np.abs(pkg.synth.bf16_bits_to_f32(d_rss[it].cpu().numpy().view(np.uint16)).astype(np.float64) - ref_rows)
         r_rms = max(1.0, float(np.sqrt((ref_rows ** 2).mean())))
-        assert e.mean() / np.abs(ref_rows).mean() <= 5e-3 and e.max() <= 2e-2 * r_rms, (it, e.mean(), e.max(), r_rms)
+        # every rank's partial travels as bf16 and the sum is rounded once more: up to half an ulp (2^-9 relative)
+        # of a value of the output's magnitude per rounding, on top of the single-GPU bound
+        bound = 2e-2 * r_rms + (world + 1) * 2.0 ** -9 * np.abs(ref_rows).max()
+        assert e.mean() / np.abs(ref_rows).mean() <= 5e-3 and e.max() <= bound, (it, e.mean(), e.max(), bound)
     # all-reduce (ring_allreduce_sum_bf16, tp_ring.hpp:253-331): every rank ends with the rank-ordered fp32 sum
     rng = np.random.default_rng(100 + rank)
     n_el = rows_local * world * H
@@ -95,8 +98,8 @@ def main():
         blk.tp_allreduce(d_buf.data_ptr(), n_el, stream)
         torch.cuda.synchronize()
         blk.synchronize()
-        allb = [torch.empty(n_el, dtype=torch.int16) for _ in range(world)]
-        dist.all_gather(allb, torch.from_numpy(mine_b.view(np.int16).copy()))
+        allb = [torch.empty(n_el * 2, dtype=torch.uint8) for _ in range(world)]
+        dist.all_gather(allb, torch.from_numpy(mine_b.view(np.uint8).copy()))
         acc = np.zeros(n_el, dtype=np.float32)
         for r in range(world):
             acc = acc + pkg.synth.bf16_bits_to_f32(allb[r].numpy().view(np.uint16))
