@@ -36,6 +36,7 @@ EXPORTS = [
     "moe_route_static", "moe_block", "moe_forward_host_submit", "moe_forward_host_wait",
     "moe_quantize_mxfp4", "moe_load_layer_f32", "moe_tp_export", "moe_tp_attach_ipc", "moe_tp_buffer", "moe_tp_attach_ptr",
     "moe_tp_forward", "moe_tp_forward_host", "moe_tp_allgather", "moe_tp_reduce_scatter", "moe_tp_allreduce",
+    "moe_load_layer_from_bin", "moe_bin_layer_offsets",
 ]
 TP_BUF_GATHER, TP_BUF_PARTIAL, TP_BUF_FLAGS, TP_BUF_TOPK_IDX, TP_BUF_TOPK_W = range(5)
 TP_N_BUFS = 5
@@ -95,6 +96,8 @@ def lib() -> C.CDLL:
         L.moe_tp_forward_host.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_uint]
         L.moe_tp_allgather.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
         L.moe_tp_reduce_scatter.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
+        L.moe_load_layer_from_bin.argtypes = [C.c_void_p, C.c_int, C.c_char_p, C.c_int, C.c_void_p]
+        L.moe_bin_layer_offsets.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
         L.moe_tp_allreduce.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
         L.moe_forward_host_submit.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_uint,
                                               C.POINTER(C.c_longlong)]
@@ -197,6 +200,13 @@ class MoeBlock:
         """fp32 expert tensors (w1 [E,2D,H], b1 [E,2D], w2 [E,H,D], b2 [E,H]) quantised to MXFP4 on the GPU."""
         arrs = [np.ascontiguousarray(a, dtype=np.float32) for a in (w1, b1, w2, b2, router_w, router_b)]
         self._check(self.L.moe_load_layer_f32(self.h, layer, *[a.ctypes.data_as(C.c_void_p) for a in arrs]))
+
+    def load_layer_from_bin(self, layer: int, path: str, file_layer: int = 0) -> np.ndarray:
+        """Loads the MoE tensors of one layer of a checkpoint in the reference's flat fp32 layout; returns the
+        layer's pre-MoE RMSNorm gain (fp32 [H])."""
+        gain = np.empty(self.H, dtype=np.float32)
+        self._check(self.L.moe_load_layer_from_bin(self.h, layer, path.encode(), file_layer, gain.ctypes.data_as(C.c_void_p)))
+        return gain
 
     def forward_host_submit(self, layer: int, t_bits: np.ndarray, out: np.ndarray, flags: int = 0) -> int:
         """Starts one batch (host arrays, ideally PinnedBuffer.array, kept alive until the wait) and returns

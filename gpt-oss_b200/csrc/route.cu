@@ -406,15 +406,16 @@ void launch_build_index(const int *topk_idx, const int *counts, int T, int E, in
 // into the tile's 512-byte scale atom, byte (r%32)*16 + (r/32)*4 + kb for row r
 // and every k block kb (the scale is per row, so the four bytes are equal).
 // ---------------------------------------------------------------------------
-constexpr int kQrThreads = 128, kQrVec = 4;   // a row of up to 128*4*8 = 4096 elements stays in registers
+constexpr int kQrWarps = 4;   // a warp per row: the row (kQrVec x 16 bytes per lane) stays in its registers
 
-__global__ void __launch_bounds__(kQrThreads)
+template <int kQrVec>         // 12: rows of up to 3072 elements, 16: up to 4096
+__global__ void __launch_bounds__(kQrWarps * 32)
 quantize_rows_kernel(const __nv_bfloat16 *__restrict__ t, const int *__restrict__ row_token,
                      const int *__restrict__ row_slot, const int *__restrict__ n_rows,
                      uint8_t *__restrict__ xq, uint8_t *__restrict__ sfa, int H) {
-  __shared__ float s_max[kQrThreads / 32];
-  const int r = blockIdx.x;
-  if (r >= *n_rows) return;
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * kQrWarps + (threadIdx.x >> 5);
+  if (r >= *n_rows) return;   // whole warps leave: no block-wide barrier below
   const int tok = row_token[r], slot = row_slot[r];
   const int tile = slot / kTileM, i2 = slot % kTileM;   // i2 = 2 * (token's place in the tile)
   const uint4 *src = reinterpret_cast<const uint4 *>(t + static_cast<size_t>(tok) * H);
@@ -423,7 +424,7 @@ quantize_rows_kernel(const __nv_bfloat16 *__restrict__ t, const int *__restrict_
   float amax = 0.f;
 #pragma unroll
   for (int u = 0; u < kQrVec; ++u) {
-    const int c = threadIdx.x + u * kQrThreads;
+    const int c = lane + u * 32;
     v[u] = c < nvec ? __ldg(src + c) : make_uint4(0u, 0u, 0u, 0u);
     const uint32_t in[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
 #pragma unroll
@@ -434,9 +435,6 @@ quantize_rows_kernel(const __nv_bfloat16 *__restrict__ t, const int *__restrict_
   }
 #pragma unroll
   for (int off = 16; off; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-  if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = amax;
-  __syncthreads();
-  amax = fmaxf(fmaxf(s_max[0], s_max[1]), fmaxf(s_max[2], s_max[3]));
   // e = floor(log2(amax)) - 7, kept where both scales stay valid UE8M0 bytes
   int e = static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu) - 127 - 7;
   e = max(-120, min(e, 120));
@@ -446,7 +444,7 @@ quantize_rows_kernel(const __nv_bfloat16 *__restrict__ t, const int *__restrict_
   uint8_t *tile_hi = xq + (static_cast<size_t>(tile) * n_kc * kTileM + i2) * kChunkK;
 #pragma unroll
   for (int u = 0; u < kQrVec; ++u) {
-    const int c = threadIdx.x + u * kQrThreads;
+    const int c = lane + u * 32;
     if (c >= nvec) break;
     const uint32_t in[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
     float f[8];
@@ -475,19 +473,23 @@ quantize_rows_kernel(const __nv_bfloat16 *__restrict__ t, const int *__restrict_
     *reinterpret_cast<uint2 *>(dst) = make_uint2(h8[0], h8[1]);
     *reinterpret_cast<uint2 *>(dst + kChunkK) = make_uint2(l8[0], l8[1]);                      // the low row follows
   }
-  if (threadIdx.x < 2) {
-    const int rr = i2 + threadIdx.x;  // row inside the tile: even = high, odd = low
-    const uint32_t byte = static_cast<uint32_t>(127 + e - 4 * static_cast<int>(threadIdx.x));
+  if (lane < 2) {
+    const int rr = i2 + lane;  // row inside the tile: even = high, odd = low
+    const uint32_t byte = static_cast<uint32_t>(127 + e - 4 * lane);
     uint8_t *atom = sfa + static_cast<size_t>(tile) * kSfAtomBytes;
     *reinterpret_cast<uint32_t *>(atom + (rr % 32) * 16 + (rr / 32) * 4) = byte * 0x01010101u;
   }
 }
 
-int quantize_rows_max_hidden() { return kQrThreads * kQrVec * 8; }
+int quantize_rows_max_hidden() { return 32 * 16 * 8; }
 
 void launch_quantize_rows(const __nv_bfloat16 *t, const int *row_token, const int *row_slot, const int *n_rows_dev,
                           uint8_t *xq, uint8_t *sfa, int H, int n_rows, cudaStream_t s) {
-  quantize_rows_kernel<<<n_rows, kQrThreads, 0, s>>>(t, row_token, row_slot, n_rows_dev, xq, sfa, H);
+  const int blocks = (n_rows + kQrWarps - 1) / kQrWarps;
+  if (H <= 32 * 12 * 8)
+    quantize_rows_kernel<12><<<blocks, kQrWarps * 32, 0, s>>>(t, row_token, row_slot, n_rows_dev, xq, sfa, H);
+  else
+    quantize_rows_kernel<16><<<blocks, kQrWarps * 32, 0, s>>>(t, row_token, row_slot, n_rows_dev, xq, sfa, H);
 }
 
 // ---------------------------------------------------------------------------

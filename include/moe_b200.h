@@ -112,6 +112,22 @@ int moe_quantize_mxfp4(const float *src_dev, size_t n_elems, uint8_t *codes_dev,
 int moe_load_layer_f32(moe_handle h, int layer, const float *w1, const float *b1, const float *w2,
                        const float *b2, const float *router_w, const float *router_b);
 
+/* moe_load_layer_f32 straight from a checkpoint file in the reference's flat fp32 layout: the Config header
+ * (run.cpp:25-45) followed by the tensors in the order of memory_map_weights (run.cpp:206-247), as
+ * export_model_bin/gpt-oss-120b/export_model_bin.py writes it and load_checkpoint (run.cpp:249-293) maps it.
+ * The MoE tensors of layer `file_layer` of the file become layer `layer` of the handle; the header's hidden,
+ * expert, intermediate and top-k sizes and swiglu_limit must be the handle's.  rms_ffn_w_out (fp32 [H], may be
+ * NULL) receives the layer's pre-MoE RMSNorm gain, which moe_block() takes as bf16.  The file is mapped
+ * read-only for the duration of the call. */
+int moe_load_layer_from_bin(moe_handle h, int layer, const char *path, int file_layer, float *rms_ffn_w_out);
+/* Where the MoE tensors of one layer start in such a file, in floats from the start of the file, from the
+ * fifteen 4-byte header fields alone (host arithmetic, no device): the order of memory_map_weights. */
+enum {
+  MOE_BIN_RMS_FFN_W = 0, MOE_BIN_ROUTER_W = 1, MOE_BIN_ROUTER_B = 2, MOE_BIN_W_MLP1 = 3, MOE_BIN_B_MLP1 = 4,
+  MOE_BIN_W_MLP2 = 5, MOE_BIN_B_MLP2 = 6, MOE_BIN_N_TENSORS = 7
+};
+int moe_bin_layer_offsets(const int32_t *header, int layer, long long offsets[MOE_BIN_N_TENSORS], long long *total_floats);
+
 /* Replaces moe_gpu()/moe_gpu_120b() as a whole (getp_run.cpp:2540, :2896), steps 0-10: the residual
  * stream rows x_dev (bf16 [rows_local, H], this rank's rows) are RMS-normalised with the bf16 gain
  * rms_w_dev [H] (rmsnorm_kernel_bf16_io, kernels/rmsnorm.hpp:115-164), go through the block (through
