@@ -536,12 +536,16 @@ combine_kernel(const __half *__restrict__ y, const int *__restrict__ topk_idx, c
                const int *__restrict__ pair_row, int T, int H, int K, __nv_bfloat16 *__restrict__ out_bf16,
                float *__restrict__ out_f32, int tp, TpPeers peers, int rows_local, int rank,
                const __nv_bfloat16 *__restrict__ residual) {
-  const int t = blockIdx.x;
+  int t = blockIdx.x;
   // tensor-parallel call: the row's bf16 partial goes straight into slot `rank` of the landing buffer of the
-  // rank that owns row t (a peer store over NVLink), which is the send half of the reduce-scatter
-  if (tp > 0)
+  // rank that owns row t (a peer store over NVLink), which is the send half of the reduce-scatter.  Blocks
+  // start with the rows of the next rank and end with this rank's own rows, so that the link is busy from the
+  // first block on and the rows that need no link fill the tail.
+  if (tp > 0) {
+    t = (t + (rank + 1) * rows_local) % T;
     out_bf16 = static_cast<__nv_bfloat16 *>(peers.partial[t / rows_local]) +
                (static_cast<ptrdiff_t>(rank) * rows_local + (t % rows_local) - t) * static_cast<ptrdiff_t>(H);
+  }
   int ex[kMaxTopK], row[kMaxTopK];
   float wt[kMaxTopK];
   for (int k = 0; k < K; ++k) {
