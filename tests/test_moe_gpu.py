@@ -16,7 +16,7 @@ Tolerances (floating point path, stated once here):
     taken relative to the output's rms, and the raw figures are printed.
   * a token whose selection differs from the oracle's (only allowed at a near-tie,
     see above) is left out of the output comparison; every other row is compared,
-    and the number of such tokens is bounded (near_tie_budget).
+    and the number of such tokens is bounded (near_tie_allowance).
   * the fp32 output kept before the final rounding: max|a-b| <= 1e-2 * max(1, rms(b))
     (the SwiGLU output feeds MLP2 as two e4m3 terms, i.e. with about 8 significant bits,
     as the reference GPU path does by rounding it to bf16).
@@ -48,7 +48,7 @@ def _load_case(name, synth):
     return layer, tokens, z
 
 
-def near_tie_budget(n_tokens):
+def near_tie_allowance(n_tokens):
     """How many tokens may select differently from the oracle because of a near-tie at the cut."""
     return max(2, n_tokens // 500)
 
@@ -63,7 +63,7 @@ def check_selection(idx, ref_idx, ref_logits):
         s = np.sort(ref_logits[t])[::-1]
         gaps = s[:k] - s[1:k + 1]                     # between neighbours of the selection, the last one at the cut
         assert gaps.min() < 1e-5, f"token {t}: selection differs with clear logit gaps {gaps}"
-    assert (~same).sum() <= near_tie_budget(len(idx)), f"{(~same).sum()} tokens select differently from the oracle"
+    assert (~same).sum() <= near_tie_allowance(len(idx)), f"{(~same).sum()} tokens select differently from the oracle"
     return same
 
 
