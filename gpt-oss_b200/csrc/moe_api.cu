@@ -37,28 +37,11 @@ int fail(moe_ctx *c, int code, const char *fmt, ...) {
                   "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__), __FILE__, __LINE__); \
   } while (0)
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void *p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  });
-  return fn;
-}
-
 // Weight tiles (LayerWeights::w1_tiles): every 16 KB tile starts with 240 rows x 64 bytes of packed e2m1 codes,
 // declared to TMA as 4-bit elements that it expands to the 8-bit containers of the block-scaled MMA
 // (16U4_ALIGN16B): dims {128 codes, 240 rows, tiles}, one box = the codes of one tile, a contiguous 15 KB read.
 int make_weight_map(moe_ctx *c, CUtensorMap *m, const uint8_t *base, size_t n_tiles) {
-  EncodeTiledFn fn = encode_fn();
+  TensorMapEncodeFn fn = tensor_map_encoder();
   if (!fn) return fail(c, MOE_ERR_CUDA, "cuTensorMapEncodeTiled not available");
   const cuuint64_t dims[3] = {kChunkK, kTileN, static_cast<cuuint64_t>(n_tiles)};
   const cuuint64_t strides[2] = {kChunkK / 2, kWTileStride};
@@ -75,7 +58,7 @@ int make_weight_map(moe_ctx *c, CUtensorMap *m, const uint8_t *base, size_t n_ti
 // k slice are one contiguous run (rows of K bytes would make the box 128 separate 128-byte pieces).  To TMA
 // this is a matrix of 128-byte rows; box = 128 x 128, 128-byte swizzle.
 int make_act_map(moe_ctx *c, CUtensorMap *m, const uint8_t *base, size_t n_tiles, int n_kc) {
-  EncodeTiledFn fn = encode_fn();
+  TensorMapEncodeFn fn = tensor_map_encoder();
   if (!fn) return fail(c, MOE_ERR_CUDA, "cuTensorMapEncodeTiled not available");
   const cuuint64_t rows = static_cast<cuuint64_t>(n_tiles) * n_kc * kTileM;
   const cuuint64_t dims[2] = {kChunkK, rows};
@@ -182,7 +165,8 @@ int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_b
   }
   if (!tpcall) {
     const int splits = router_splits(T, H, c->sm_count);
-    launch_router_partials(t, w.router_w3, c->router_part, T, H, E, splits, s);
+    if (!launch_router_partials(t, w.tm_router, c->router_part, T, H, E, splits, status, s))
+      return fail(c, MOE_ERR_INVALID, "no tensor map for the input rows (16-byte aligned, hidden_dim a multiple of 8?)");
     mark();
     launch_topk_softmax(c->logits, c->router_part, splits, w.router_b, T, E, K, c->topk_idx, c->topk_w, c->counts, s);
     mark();
@@ -203,7 +187,8 @@ int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_b
     }
     CU_TRY(c, cudaEventRecord(c->ev_join, c->aux_stream));
     const int splits = router_splits(tp_rows_local, H, c->sm_count);
-    launch_router_partials(t_local, w.router_w3, c->router_part, tp_rows_local, H, E, splits, s);
+    if (!launch_router_partials(t_local, w.tm_router, c->router_part, tp_rows_local, H, E, splits, status, s))
+      return fail(c, MOE_ERR_INVALID, "no tensor map for the input rows (16-byte aligned, hidden_dim a multiple of 8?)");
     mark();
     launch_topk_softmax(c->logits, c->router_part, splits, w.router_b, tp_rows_local, E, K, nullptr, nullptr, nullptr, s,
                         tp, &c->peers, rank * tp_rows_local);
@@ -339,15 +324,15 @@ int moe_create(const moe_config *cfg, moe_handle *out) {
   c->sm_count = prop.multiProcessorCount;
   CU_TRY(c, cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
   CU_TRY(c, expert_gemm_init());
-  CU_TRY(c, route_init());
+  CU_TRY(c, router_init());
 
   const size_t T = c->max_rows, P = c->max_pairs;
   int rc;
   if ((rc = dev_alloc(c, &c->t_in, T * c->H))) return rc;
   if ((rc = dev_alloc(c, &c->t_norm, T * c->H))) return rc;
   if ((rc = dev_alloc(c, &c->logits, T * c->E))) return rc;
-  // splits * rows never exceeds (sm_count / tiles) * 64 * tiles = 64 * sm_count
-  if ((rc = dev_alloc(c, &c->router_part, std::max<size_t>(T, 64 * static_cast<size_t>(c->sm_count) + 64) * c->E))) return rc;
+  // splits * rows never exceeds (sm_count / tiles) * 128 * tiles = 128 * sm_count
+  if ((rc = dev_alloc(c, &c->router_part, std::max<size_t>(T, 128 * static_cast<size_t>(c->sm_count) + 128) * c->E))) return rc;
   if ((rc = dev_alloc(c, &c->topk_idx, T * c->K))) return rc;
   if ((rc = dev_alloc(c, &c->topk_w, T * c->K))) return rc;
   if ((rc = dev_alloc(c, &c->counts, (size_t)c->E))) return rc;
@@ -522,6 +507,8 @@ int moe_load_layer(moe_handle c, int layer, const uint8_t *w1_codes, const uint8
   CU_TRY(c, cudaMemcpy(w.router_b, router_b, static_cast<size_t>(E) * 4, cudaMemcpyHostToDevice));
   if ((rc = make_weight_map(c, &w.tm_w1, w.w1_tiles, static_cast<size_t>(E) * n_nt1 * n_kc1))) return rc;
   if ((rc = make_weight_map(c, &w.tm_w2, w.w2_tiles, static_cast<size_t>(E) * n_nt2 * n_kc2))) return rc;
+  if (!make_router_weight_map(&w.tm_router, w.router_w3, E, H))
+    return fail(c, MOE_ERR_CUDA, "cuTensorMapEncodeTiled(router weight, %d x %d) failed", E, H);
   w.loaded = true;
   return MOE_OK;
 }

@@ -7,6 +7,7 @@
 #include <stdint.h>
 
 #include <algorithm>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -114,7 +115,7 @@ struct LayerWeights {
   uint8_t *w2_scales_raw = nullptr;  // [E, H, Dl/32]
   __nv_bfloat16 *router_w3 = nullptr;  // [3][E][H] exact 3-way bf16 split of the fp32 router weight
   float *router_b = nullptr;           // [E]
-  CUtensorMap tm_w1, tm_w2;
+  CUtensorMap tm_w1, tm_w2, tm_router;
 };
 
 }  // namespace moe
@@ -181,11 +182,31 @@ struct moe_ctx {
 
 namespace moe {
 
-// route.cu
-cudaError_t route_init();   // per-device kernel attributes; call with the device current
+// cuTensorMapEncodeTiled through the runtime's driver entry point table (no link against libcuda).
+typedef CUresult (*TensorMapEncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                      const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                      CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+inline TensorMapEncodeFn tensor_map_encoder() {
+  static TensorMapEncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<TensorMapEncodeFn>(p);
+  });
+  return fn;
+}
+
+// router_sm100.cu
+cudaError_t router_init();   // per-device kernel attributes; call with the device current
 int router_splits(int T, int H, int sm_count);
-void launch_router_partials(const __nv_bfloat16 *t, const __nv_bfloat16 *w3, float *partial, int T, int H, int E,
-                            int splits, cudaStream_t s);
+int router_chunks(int H);
+bool make_router_weight_map(CUtensorMap *m, const __nv_bfloat16 *w3, int E, int H);
+bool launch_router_partials(const __nv_bfloat16 *t, const CUtensorMap &tm_w, float *partial, int T, int H, int E,
+                            int splits, unsigned int *status, cudaStream_t s);
+// route.cu
 void launch_topk_softmax(float *logits, const float *partial, int splits, const float *bias, int T, int E, int K,
                          int *idx, float *w, int *counts, cudaStream_t s, int tp = 0, const TpPeers *peers = nullptr,
                          int row_offset = 0);

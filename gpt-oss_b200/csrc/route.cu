@@ -1,4 +1,4 @@
-// Routing side of the MoE block: router logits, top-k + softmax, expert
+// Routing side of the MoE block (the router GEMM itself is router_sm100.cu): top-k + softmax, expert
 // histogram, stable token->expert permutation, work list of the grouped GEMM,
 // row gather and the weighted un-permute.  Everything stays on the device: the
 // reference's per-layer host round trip (expert counts copied to the host, tile
@@ -13,143 +13,6 @@
 #include "moe_internal.cuh"
 
 namespace moe {
-
-// ---------------------------------------------------------------------------
-// Router logits: logits[t, e] = sum_k t[t, k] * Wr[e, k] + br[e], fp32.
-// Reference: matmul + bias of run.cpp:660-669 (double accumulation of float
-// products); the reference GPU path rounds the logits to bf16
-// (getp_run.cpp:2612-2620), which this path deliberately does not.
-//
-// The fp32 router weight is pre-split at load time into three bf16 planes
-// (hi + mid + lo == w exactly, 8+8+8 significand bits), so each plane times a
-// bf16 activation is an exact fp32 product and the sum runs on the tensor
-// cores (mma.sync m16n8k16, fp32 accumulate).  A block owns 64 tokens x up to
-// 128 experts x one slice of k (split-k keeps all SMs busy at decode batch
-// sizes); operands are staged through shared memory with cp.async, double
-// buffered.  Each slice writes its partial sums; topk_softmax_kernel adds the
-// slices in a fixed order in double precision, so results do not depend on
-// scheduling.
-// ---------------------------------------------------------------------------
-constexpr int kRtTok = 64, kRtExp = 128, kRtK = 64, kRtThreads = 256;
-constexpr int kRtPitch = kRtK * 2 + 16;                 // bytes per staged row: 64 bf16 + pad (no bank conflicts)
-constexpr int kRtXBytes = kRtTok * kRtPitch;            // 9216
-constexpr int kRtWBytes = 3 * kRtExp * kRtPitch;        // 55296
-constexpr int kRtStage = kRtXBytes + kRtWBytes;         // 64512
-constexpr int kRtSmem = 2 * kRtStage;                   // 129024
-
-__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, bool valid) {
-  const int sz = valid ? 16 : 0;  // size 0: the 16 destination bytes are zero-filled
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(sz) : "memory");
-}
-
-// partial[(split * T + tok) * E + e]
-__global__ void __launch_bounds__(kRtThreads)
-router_partial_kernel(const __nv_bfloat16 *__restrict__ t, const __nv_bfloat16 *__restrict__ w3,
-                      float *__restrict__ partial, int T, int H, int E, int chunks_per_split) {
-  extern __shared__ __align__(16) uint8_t rt_smem[];
-  const uint32_t sbase = static_cast<uint32_t>(__cvta_generic_to_shared(rt_smem));
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int g = lane >> 2, q = lane & 3;
-  const int tok0 = blockIdx.x * kRtTok, e0 = blockIdx.z * kRtExp;
-  const int n_chunks = H / kRtK + ((H % kRtK) ? 1 : 0);
-  const int c_begin = blockIdx.y * chunks_per_split, c_end = min(n_chunks, c_begin + chunks_per_split);
-  const size_t plane = static_cast<size_t>(E) * H;
-  const int mt = warp & 3, nh = warp >> 2;  // 16-token tile, 64-expert half
-
-  float acc[8][4];
-#pragma unroll
-  for (int n = 0; n < 8; ++n)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
-
-  auto issue = [&](int chunk, int buf) {
-    const int k0 = chunk * kRtK;
-    const uint32_t xs = sbase + buf * kRtStage, ws = xs + kRtXBytes;
-    // 8 x 16-byte pieces per row
-    for (int i = threadIdx.x; i < kRtTok * 8; i += kRtThreads) {
-      const int r = i >> 3, p = i & 7;
-      const bool ok = (tok0 + r < T) && (k0 + p * 8 < H);
-      cp_async16(xs + r * kRtPitch + p * 16, t + static_cast<size_t>(min(tok0 + r, T - 1)) * H + min(k0 + p * 8, H - 8), ok);
-    }
-    for (int i = threadIdx.x; i < 3 * kRtExp * 8; i += kRtThreads) {
-      const int pl = i / (kRtExp * 8), rem = i % (kRtExp * 8), r = rem >> 3, p = rem & 7;
-      const bool ok = (e0 + r < E) && (k0 + p * 8 < H);
-      cp_async16(ws + (pl * kRtExp + r) * kRtPitch + p * 16,
-                 w3 + pl * plane + static_cast<size_t>(min(e0 + r, E - 1)) * H + min(k0 + p * 8, H - 8), ok);
-    }
-    asm volatile("cp.async.commit_group;" ::: "memory");
-  };
-
-  if (c_begin < c_end) issue(c_begin, 0);
-  for (int c = c_begin; c < c_end; ++c) {
-    const int buf = (c - c_begin) & 1;
-    if (c + 1 < c_end) {
-      issue(c + 1, buf ^ 1);
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-    }
-    __syncthreads();
-    const uint8_t *xs = rt_smem + buf * kRtStage, *ws = xs + kRtXBytes;
-#pragma unroll
-    for (int ks = 0; ks < kRtK / 16; ++ks) {
-      const int kb = ks * 32 + q * 4;  // byte offset of (k0 + 16 ks + 2q) in a staged row
-      uint32_t a[4];
-      const uint8_t *xr = xs + (mt * 16 + g) * kRtPitch + kb;
-      a[0] = *reinterpret_cast<const uint32_t *>(xr);
-      a[1] = *reinterpret_cast<const uint32_t *>(xr + 8 * kRtPitch);
-      a[2] = *reinterpret_cast<const uint32_t *>(xr + 16);
-      a[3] = *reinterpret_cast<const uint32_t *>(xr + 8 * kRtPitch + 16);
-#pragma unroll
-      for (int n = 0; n < 8; ++n) {
-#pragma unroll
-        for (int pl = 0; pl < 3; ++pl) {
-          const uint8_t *wr = ws + (pl * kRtExp + nh * 64 + n * 8 + g) * kRtPitch + kb;
-          mma_bf16_16816(acc[n], a, *reinterpret_cast<const uint32_t *>(wr), *reinterpret_cast<const uint32_t *>(wr + 16));
-        }
-      }
-    }
-    __syncthreads();
-  }
-  float *out = partial + static_cast<size_t>(blockIdx.y) * T * E;
-#pragma unroll
-  for (int n = 0; n < 8; ++n) {
-    const int e = e0 + nh * 64 + n * 8 + 2 * q;
-    const int r0 = tok0 + mt * 16 + g, r1 = r0 + 8;
-    if (e < E) {  // E is even (checked by the launcher), so e + 1 < E as well
-      if (r0 < T) *reinterpret_cast<float2 *>(out + static_cast<size_t>(r0) * E + e) = make_float2(acc[n][0], acc[n][1]);
-      if (r1 < T) *reinterpret_cast<float2 *>(out + static_cast<size_t>(r1) * E + e) = make_float2(acc[n][2], acc[n][3]);
-    }
-  }
-}
-
-int router_splits(int T, int H, int sm_count) {
-  const int tiles = (T + kRtTok - 1) / kRtTok, n_chunks = (H + kRtK - 1) / kRtK;
-  int splits = max(1, min(min(16, n_chunks), sm_count / tiles));
-  const int cps = (n_chunks + splits - 1) / splits;
-  return (n_chunks + cps - 1) / cps;  // every split gets at least one chunk
-}
-
-// The router stages more shared memory than a kernel gets by default.  The limit is a property of the
-// (kernel, device) pair, so every device a handle is created on sets it for itself (moe_create calls this
-// with that device current); a flag shared by the whole process would leave the launch rejected on every
-// GPU but the first one a one-process, one-thread-per-GPU caller touches.
-cudaError_t route_init() {
-  return cudaFuncSetAttribute(router_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kRtSmem);
-}
-
-void launch_router_partials(const __nv_bfloat16 *t, const __nv_bfloat16 *w3, float *partial, int T, int H, int E,
-                            int splits, cudaStream_t s) {
-  const int n_chunks = (H + kRtK - 1) / kRtK, cps = (n_chunks + splits - 1) / splits;
-  dim3 grid((T + kRtTok - 1) / kRtTok, splits, (E + kRtExp - 1) / kRtExp);
-  router_partial_kernel<<<grid, kRtThreads, kRtSmem, s>>>(t, w3, partial, T, H, E, cps);
-}
 
 // ---------------------------------------------------------------------------
 // Top-k + softmax over the selected logits + expert histogram.  One warp per
@@ -732,11 +595,13 @@ extern "C" int moe_route_static(moe_handle c, int layer, const void *t_dev, int 
   int splits = router_splits(rows, c->H, c->sm_count);
   const int fit = static_cast<int>(kStaticRouteFloats / per_slice);
   if (splits > fit) {
-    const int n_chunks = (c->H + kRtK - 1) / kRtK, cps = (n_chunks + fit - 1) / fit;
+    const int n_chunks = router_chunks(c->H), cps = (n_chunks + fit - 1) / fit;
     splits = (n_chunks + cps - 1) / cps;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  launch_router_partials(static_cast<const __nv_bfloat16 *>(t_dev), w.router_w3, scratch, rows, c->H, c->E, splits, s);
+  if (!launch_router_partials(static_cast<const __nv_bfloat16 *>(t_dev), w.tm_router, scratch, rows, c->H, c->E, splits,
+                              c->status, s))
+    return fail(MOE_ERR_INVALID, "moe_route_static: no tensor map for the rows (16-byte aligned, hidden_dim a multiple of 8?)");
   launch_topk_softmax(logits_dev, scratch, splits, w.router_b, rows, c->E, c->K, idx_dev, w_dev, nullptr, s);
   c->launches += 2;
   if (cudaGetLastError() != cudaSuccess) return fail(MOE_ERR_CUDA, "moe_route_static: kernel launch failed");
