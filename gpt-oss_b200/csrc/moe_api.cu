@@ -163,12 +163,32 @@ int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_b
     t = c->t_norm;
     c->launches += 1;
   }
+  // Routing of `n` rows at `src`: one fused launch (router GEMM, bias, top-k, softmax, histogram) when the
+  // experts fit one CTA, else partial sums and topk_softmax_kernel.  In a TP call the selection goes to the
+  // top-k buffers of every rank at this rank's row offset and the histogram is taken after the exchange.
+  auto route_rows = [&](const __nv_bfloat16 *src, int n) -> int {
+    const int slices = (flags & MOE_FWD_SPLIT_ROUTER) ? 0 : router_fused_slices(n, H, E, c->sm_count, c->router_cluster);
+    RouteOut ro = {};
+    ro.logits = c->logits; ro.bias = w.router_b; ro.K = K;
+    if (tpcall) { ro.tp = tp; ro.peers = c->peers; ro.row_offset = rank * tp_rows_local; }
+    else { ro.idx = c->topk_idx; ro.w = c->topk_w; ro.counts = c->counts; }
+    bool ok;
+    if (slices > 0) {
+      ok = launch_router_fused(src, w.tm_router, n, H, E, slices, ro, status, s);
+      mark();
+      c->launches -= 1;   // one launch where the tally below counts two
+    } else {
+      const int splits = router_splits(n, H, c->sm_count);
+      ok = launch_router_partials(src, w.tm_router, c->router_part, n, H, E, splits, status, s);
+      mark();
+      launch_topk_softmax(ro.logits, c->router_part, splits, ro.bias, n, E, K, ro.idx, ro.w, ro.counts, s, ro.tp,
+                          &ro.peers, ro.row_offset);
+    }
+    if (!ok) return fail(c, MOE_ERR_INVALID, "router launch refused (input rows 16-byte aligned, hidden_dim a multiple of 8?)");
+    return MOE_OK;
+  };
   if (!tpcall) {
-    const int splits = router_splits(T, H, c->sm_count);
-    if (!launch_router_partials(t, w.tm_router, c->router_part, T, H, E, splits, status, s))
-      return fail(c, MOE_ERR_INVALID, "no tensor map for the input rows (16-byte aligned, hidden_dim a multiple of 8?)");
-    mark();
-    launch_topk_softmax(c->logits, c->router_part, splits, w.router_b, T, E, K, c->topk_idx, c->topk_w, c->counts, s);
+    if (int rc = route_rows(t, T)) return rc;
     mark();
   } else {
     // all-gather push of this rank's rows on the side stream, beside the routing of the same rows
@@ -186,12 +206,7 @@ int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_b
       launch_tp_allgather_push(t_local, tp_rows_local, H, c->peers, tp, rank, c->sm_count, c->aux_stream);
     }
     CU_TRY(c, cudaEventRecord(c->ev_join, c->aux_stream));
-    const int splits = router_splits(tp_rows_local, H, c->sm_count);
-    if (!launch_router_partials(t_local, w.tm_router, c->router_part, tp_rows_local, H, E, splits, status, s))
-      return fail(c, MOE_ERR_INVALID, "no tensor map for the input rows (16-byte aligned, hidden_dim a multiple of 8?)");
-    mark();
-    launch_topk_softmax(c->logits, c->router_part, splits, w.router_b, tp_rows_local, E, K, nullptr, nullptr, nullptr, s,
-                        tp, &c->peers, rank * tp_rows_local);
+    if (int rc = route_rows(t_local, tp_rows_local)) return rc;
     CU_TRY(c, cudaStreamWaitEvent(s, c->ev_join, 0));
     launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, 0, c->tp_epoch, status, s);
     launch_count_experts(c->topk_idx, T * K, E, c->counts, s);
@@ -324,7 +339,7 @@ int moe_create(const moe_config *cfg, moe_handle *out) {
   c->sm_count = prop.multiProcessorCount;
   CU_TRY(c, cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
   CU_TRY(c, expert_gemm_init());
-  CU_TRY(c, router_init());
+  CU_TRY(c, router_init(&c->router_cluster));
 
   const size_t T = c->max_rows, P = c->max_pairs;
   int rc;

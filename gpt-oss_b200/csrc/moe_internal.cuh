@@ -129,6 +129,7 @@ struct moe_ctx {
   int joff;       // d0 - k0: column of the shard's first SwiGLU output inside that window
   int max_rows, max_pairs;
   int sm_count;
+  int router_cluster = 0;   // largest thread-block cluster the fused router kernel can use on this device (0: none)
   cudaStream_t stream = nullptr;  // used by moe_forward_host
   std::vector<moe::LayerWeights> layers;
 
@@ -199,8 +200,25 @@ inline TensorMapEncodeFn tensor_map_encoder() {
   return fn;
 }
 
+// What the fused router kernel writes: logits [rows, E], and the selection, weights and expert histogram
+// exactly as topk_softmax_kernel does (to every rank's top-k buffers when tp > 0, at row_offset).
+struct RouteOut {
+  float *logits;
+  const float *bias;
+  int K;
+  int *idx;
+  float *w;
+  int *counts;
+  int tp;
+  int row_offset;
+  TpPeers peers;
+};
+
 // router_sm100.cu
-cudaError_t router_init();   // per-device kernel attributes; call with the device current
+cudaError_t router_init(int *max_cluster);   // per-device kernel attributes; call with the device current
+int router_fused_slices(int T, int H, int E, int sm_count, int max_cluster);
+bool launch_router_fused(const __nv_bfloat16 *t, const CUtensorMap &tm_w, int T, int H, int E, int slices,
+                         const RouteOut &ro, unsigned int *status, cudaStream_t s);
 int router_splits(int T, int H, int sm_count);
 int router_chunks(int H);
 bool make_router_weight_map(CUtensorMap *m, const __nv_bfloat16 *w3, int E, int H);

@@ -11,19 +11,14 @@
 #include <mutex>
 
 #include "moe_internal.cuh"
+#include "route_select.cuh"
 
 namespace moe {
 
 // ---------------------------------------------------------------------------
 // Top-k + softmax over the selected logits + expert histogram.  One warp per
-// token.  Reference: topk (run.cpp:387-420) then softmax (run.cpp:335-353,
-// :674); GPU counterpart route_select_softmax_kernel_bf16io
-// (kernels/moe.hpp:465-561) and count_tokens_per_expert_kernel (:744).
-// Selection is exact: plain fp32 comparisons, equal values resolved towards
-// the lower index (kernels/moe.hpp:333-342).  Weights stay fp32.
+// token; the selection itself is select_softmax_store (route_select.cuh).
 // ---------------------------------------------------------------------------
-constexpr int kMaxExpPerLane = 8;  // E <= 256
-constexpr int kMaxTopK = 8;
 
 // With `partial` set, the logits are first formed from the router's split-k partial sums: slices added
 // in ascending order in double precision, rounded to float, then the bias added in float
@@ -45,9 +40,17 @@ __global__ void topk_softmax_kernel(float *__restrict__ logits, const float *__r
     const int e = lane + 32 * i;
     if (e < E) {
       if (partial != nullptr) {
+        // the first 16 slices (router_splits() never makes more) are loaded together, then added in order
+        const float *col = partial + static_cast<size_t>(warp) * E + e;
+        const size_t slice = static_cast<size_t>(T) * E;
+        float p[16];
+#pragma unroll
+        for (int sp = 0; sp < 16; ++sp) p[sp] = sp < splits ? col[sp * slice] : 0.f;
         double sum = 0.0;
-        for (int sp = 0; sp < splits; ++sp)
-          sum += static_cast<double>(partial[(static_cast<size_t>(sp) * T + warp) * E + e]);
+#pragma unroll
+        for (int sp = 0; sp < 16; ++sp)
+          if (sp < splits) sum += static_cast<double>(p[sp]);
+        for (int sp = 16; sp < splits; ++sp) sum += static_cast<double>(col[sp * slice]);
         v[i] = __fadd_rn(static_cast<float>(sum), bias[e]);
         row[e] = v[i];
       } else {
@@ -58,49 +61,7 @@ __global__ void topk_softmax_kernel(float *__restrict__ logits, const float *__r
       taken |= 1u << i;
     }
   }
-  float sel_v = 0.f;  // lane k keeps the k-th selected logit
-  int sel_i = 0;
-  for (int k = 0; k < K; ++k) {
-    float bv = 0.f;
-    int bi = -1;
-#pragma unroll
-    for (int i = 0; i < kMaxExpPerLane; ++i) {
-      if (taken & (1u << i)) continue;
-      if (bi < 0 || v[i] > bv) { bv = v[i]; bi = lane + 32 * i; }  // ascending e: ties keep the lower index
-    }
-#pragma unroll
-    for (int off = 16; off; off >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
-      if (oi >= 0 && (bi < 0 || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
-    }
-    if (bi >= 0 && (bi & 31) == lane) taken |= 1u << (bi >> 5);
-    if (lane == k) { sel_v = bv; sel_i = bi; }
-  }
-  // softmax over the K selected values, double max/sum as in run.cpp:335-353
-  double mx = -1e300;
-  for (int k = 0; k < K; ++k) {
-    const float vk = __shfl_sync(0xffffffffu, sel_v, k);
-    mx = fmax(mx, static_cast<double>(vk));
-  }
-  float ex = 0.f;
-  if (lane < K) ex = expf(static_cast<float>(static_cast<double>(sel_v) - mx));
-  double sum = 0.0;
-  for (int k = 0; k < K; ++k) sum += static_cast<double>(__shfl_sync(0xffffffffu, ex, k));
-  if (lane < K) {
-    const float wt = static_cast<float>(static_cast<double>(ex) / sum);
-    const size_t o = static_cast<size_t>(row_offset + warp) * K + lane;
-    if (tp > 0) {
-      for (int r = 0; r < tp; ++r) {
-        static_cast<int *>(peers.topk_idx[r])[o] = sel_i;
-        static_cast<float *>(peers.topk_w[r])[o] = wt;
-      }
-    } else {
-      idx[o] = sel_i;
-      w[o] = wt;
-    }
-    if (counts != nullptr && sel_i >= 0) atomicAdd(&counts[sel_i], 1);
-  }
+  select_softmax_store(v, taken, lane, K, static_cast<size_t>(row_offset + warp), idx, w, counts, tp, peers);
 }
 
 // Expert histogram over an already exchanged selection (count_tokens_per_expert_kernel,

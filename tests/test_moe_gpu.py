@@ -102,7 +102,7 @@ def run_block(pkg, layer, tokens, flags=0, max_rows=None, keep_f32=True):
     return blk, out
 
 
-@pytest.mark.parametrize("flags", [0, 1], ids=["tcgen05", "simt"])
+@pytest.mark.parametrize("flags", [0, 1, 4], ids=["tcgen05", "simt", "split_router"])
 @pytest.mark.parametrize("name", golden_cases())
 def test_golden_fixture(name, flags, pkg, synth):
     layer, tokens, z = _load_case(name, synth)
@@ -181,11 +181,33 @@ def test_shapes_against_oracle(E, H, D, T, zipf, pkg, synth, port):
     layer = synth.make_layer(E, H, D, seed=E + T, zipf_s=zipf)
     tokens = synth.make_tokens(T, H, seed=H + T)
     ref_logits, ref_i, ref_w, ref_out = port.moe_layer(layer, tokens)
-    for flags in (0, 1):
+    for flags in (0, 1, 4):
         blk, out = run_block(pkg, layer, tokens, flags=flags)
         try:
             same = check_selection(blk.debug(pkg.DBG_TOPK_IDX), ref_i, ref_logits)
             check_output(out, blk.debug(pkg.DBG_OUT_F32), ref_out, synth, rows=same)
+        finally:
+            blk.close()
+
+
+@pytest.mark.parametrize("E,T", [(128, 1), (128, 130), (128, 1000), (128, 3000), (128, 10000), (32, 700), (24, 257),
+                                 (256, 300)])
+def test_router_forms_against_oracle(E, T, pkg, synth, port):
+    """Router logits, selection, weights and histogram of the fused cluster kernel (1 to 8 k slices per token
+    tile, by row count) and of the two-launch form (always taken above 128 experts), each against the oracle."""
+    H, D = 576, 64   # nine 64-wide k chunks: eight slices leave some CTAs of a cluster without a chunk
+    layer = synth.make_layer(E, H, D, seed=3 * E + T, zipf_s=1.1)
+    tokens = synth.make_tokens(T, H, seed=T)
+    ref_logits, ref_i, ref_w, _ = port.moe_layer(layer, tokens)
+    for flags in (0, pkg.FWD_SPLIT_ROUTER):
+        blk, _ = run_block(pkg, layer, tokens, flags=flags)
+        try:
+            logits = blk.debug(pkg.DBG_LOGITS)
+            np.testing.assert_allclose(logits, ref_logits, rtol=0, atol=2e-5 * max(1.0, np.abs(ref_logits).max()))
+            idx = blk.debug(pkg.DBG_TOPK_IDX)
+            same = check_selection(idx, ref_i, ref_logits)
+            np.testing.assert_allclose(blk.debug(pkg.DBG_TOPK_W)[same], ref_w[same], rtol=2e-5, atol=1e-7)
+            assert np.array_equal(blk.debug(pkg.DBG_COUNTS), np.bincount(idx.ravel(), minlength=E))
         finally:
             blk.close()
 
