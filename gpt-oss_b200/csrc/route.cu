@@ -139,7 +139,7 @@ build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ cou
 
   // Stable compaction in ascending token order.  Warp w owns the contiguous token range [w*per, (w+1)*per):
   // a first walk counts the range's hits with ballots, one block-wide barrier turns the eight counts into
-  // starting positions, a second walk (the selections are still in L1) writes the rows.  No barrier per step.
+  // starting positions, a second walk writes the rows.  No barrier per step.
   const int per = ((T + 7) / 8 + 31) / 32 * 32;       // tokens per warp, whole ballot steps
   const int t_begin = warp * per, t_end = min(T, t_begin + per);
   auto hit_of = [&](int t) -> int {
@@ -152,8 +152,16 @@ build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ cou
       if (topk_idx[static_cast<size_t>(t) * K + k] == e) return k;
     return -1;
   };
+  // the first kCached ballot steps of the range (all of it up to 2048 tokens) are loaded at once and kept
+  constexpr int kCached = 8;
+  int cached[kCached];
+#pragma unroll
+  for (int j = 0; j < kCached; ++j) cached[j] = hit_of(t_begin + 32 * j + lane);
+  const int t_rest = t_begin + 32 * kCached;
   int mine = 0;
-  for (int t0 = t_begin; t0 < t_end; t0 += 32) mine += __popc(__ballot_sync(0xffffffffu, hit_of(t0 + lane) >= 0));
+#pragma unroll
+  for (int j = 0; j < kCached; ++j) mine += __popc(__ballot_sync(0xffffffffu, cached[j] >= 0));
+  for (int t0 = t_rest; t0 < t_end; t0 += 32) mine += __popc(__ballot_sync(0xffffffffu, hit_of(t0 + lane) >= 0));
   if (lane == 0) s_warp[warp] = mine;
   __syncthreads();
   int before = 0, total_hits = 0;
@@ -162,9 +170,7 @@ build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ cou
     before += i < warp ? s_warp[i] : 0;
     total_hits += s_warp[i];
   }
-  for (int t0 = t_begin; t0 < t_end; t0 += 32) {
-    const int t = t0 + lane;
-    const int hit = hit_of(t);
+  auto place = [&](int t, int hit) {
     const unsigned m = __ballot_sync(0xffffffffu, hit >= 0);
     if (hit >= 0) {
       const int pos = before + __popc(m & ((1u << lane) - 1u));
@@ -179,7 +185,10 @@ build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ cou
       }
     }
     before += __popc(m);
-  }
+  };
+#pragma unroll
+  for (int j = 0; j < kCached; ++j) place(t_begin + 32 * j + lane, cached[j]);
+  for (int t0 = t_rest; t0 < t_end; t0 += 32) place(t0 + lane, hit_of(t0 + lane));
   if (tid == 0 && total_hits != cnt) atomicOr(status, ST_BAD_INDEX);
 
   // work items: one per (token tile of kTokTile rows, block of kTileN weight rows); items that share a
@@ -355,11 +364,16 @@ void launch_gather_rows(const __nv_bfloat16 *t, const int *row_token, const int 
 // order and rounding of run.cpp:678 / :738-741.  GPU counterpart:
 // reduce_tokenwise_expert_outputs_bf16_bf16wts (kernels/moe.hpp:700-730).
 // ---------------------------------------------------------------------------
+// The expert rows of one step are all requested before the first is used, and the next step's while this
+// one is finished.  kK: experts per token known at compile time, 0: any K up to kMaxTopK (predicated).
+template <int kK>
 __global__ void __launch_bounds__(128)
 combine_kernel(const __half *__restrict__ y, const int *__restrict__ topk_idx, const float *__restrict__ topk_w,
                const int *__restrict__ pair_row, int T, int H, int K, __nv_bfloat16 *__restrict__ out_bf16,
                float *__restrict__ out_f32, int tp, TpPeers peers, int rows_local, int rank,
                const __nv_bfloat16 *__restrict__ residual) {
+  constexpr int kSlots = kK > 0 ? kK : kMaxTopK;
+  if (kK > 0) K = kK;
   int t = blockIdx.x;
   // tensor-parallel call: the row's bf16 partial goes straight into slot `rank` of the landing buffer of the
   // rank that owns row t (a peer store over NVLink), which is the send half of the reduce-scatter.  Blocks
@@ -370,34 +384,56 @@ combine_kernel(const __half *__restrict__ y, const int *__restrict__ topk_idx, c
     out_bf16 = static_cast<__nv_bfloat16 *>(peers.partial[t / rows_local]) +
                (static_cast<ptrdiff_t>(rank) * rows_local + (t % rows_local) - t) * static_cast<ptrdiff_t>(H);
   }
-  int ex[kMaxTopK], row[kMaxTopK];
-  float wt[kMaxTopK];
-  for (int k = 0; k < K; ++k) {
-    ex[k] = topk_idx[static_cast<size_t>(t) * K + k];
-    wt[k] = topk_w[static_cast<size_t>(t) * K + k];
-    row[k] = pair_row[static_cast<size_t>(t) * K + k];
-  }
-  for (int i = 1; i < K; ++i)  // insertion sort by expert index
-    for (int j = i; j > 0 && ex[j] < ex[j - 1]; --j) {
-      int a = ex[j]; ex[j] = ex[j - 1]; ex[j - 1] = a;
-      a = row[j]; row[j] = row[j - 1]; row[j - 1] = a;
-      float f = wt[j]; wt[j] = wt[j - 1]; wt[j - 1] = f;
+  int ex[kSlots], row[kSlots];
+  float wt[kSlots];
+#pragma unroll
+  for (int k = 0; k < kSlots; ++k) {
+    if (k < K) {
+      ex[k] = topk_idx[static_cast<size_t>(t) * K + k];
+      wt[k] = topk_w[static_cast<size_t>(t) * K + k];
+      row[k] = pair_row[static_cast<size_t>(t) * K + k];
+    } else {
+      ex[k] = 0x7fffffff; wt[k] = 0.f; row[k] = 0;
     }
-  // 16 bytes (8 values) per thread and expert row: the K loads of an iteration are in flight together
-  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
+  }
+#pragma unroll
+  for (int i = 1; i < kSlots; ++i)  // sort by expert index (a fixed network of compare-exchanges: registers only)
+#pragma unroll
+    for (int j = kSlots - 1; j >= i; --j)
+      if (ex[j] < ex[j - 1]) {
+        int a = ex[j]; ex[j] = ex[j - 1]; ex[j - 1] = a;
+        a = row[j]; row[j] = row[j - 1]; row[j - 1] = a;
+        float f = wt[j]; wt[j] = wt[j - 1]; wt[j - 1] = f;
+      }
+  const uint4 *src[kSlots];
+#pragma unroll
+  for (int k = 0; k < kSlots; ++k) src[k] = reinterpret_cast<const uint4 *>(y + static_cast<size_t>(row[k]) * H);
+  // 16 bytes (8 values) per thread and expert row
+  const int n_vec = H / 8;
+  uint4 raw[kSlots];
+  auto fetch = [&](int i) {
+#pragma unroll
+    for (int k = 0; k < kSlots; ++k)
+      if (k < K && i < n_vec) raw[k] = __ldg(src[k] + i);
+  };
+  fetch(threadIdx.x);
+  for (int i = threadIdx.x; i < n_vec; i += blockDim.x) {
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-    for (int k = 0; k < K; ++k) {
-      const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(y + static_cast<size_t>(row[k]) * H) + i);
-      const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 v = __half22float2(*reinterpret_cast<const __half2 *>(&w4[j]));
-        acc[2 * j] = __fadd_rn(acc[2 * j], __fmul_rn(v.x, wt[k]));
-        acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], __fmul_rn(v.y, wt[k]));
+    for (int k = 0; k < kSlots; ++k) {
+      if (k < K) {
+        const uint32_t w4[4] = {raw[k].x, raw[k].y, raw[k].z, raw[k].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 v = __half22float2(*reinterpret_cast<const __half2 *>(&w4[j]));
+          acc[2 * j] = __fadd_rn(acc[2 * j], __fmul_rn(v.x, wt[k]));
+          acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], __fmul_rn(v.y, wt[k]));
+        }
       }
     }
+    fetch(i + blockDim.x);   // the next step's rows are on their way while this one is finished and stored
     if (out_f32 != nullptr) {
       float4 *o = reinterpret_cast<float4 *>(out_f32 + static_cast<size_t>(t) * H) + 2 * i;
       o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
@@ -429,8 +465,8 @@ void launch_combine(const __half *y, const int *topk_idx, const float *topk_w, c
                     int rows_local, int rank, const __nv_bfloat16 *residual) {
   TpPeers pv = {};
   if (tp > 0 && peers != nullptr) pv = *peers;
-  combine_kernel<<<T, 128, 0, s>>>(y, topk_idx, topk_w, pair_row, T, H, K, out_bf16, out_f32, tp, pv, rows_local, rank,
-                                   residual);
+  auto kernel = K == 4 ? combine_kernel<4> : combine_kernel<0>;
+  kernel<<<T, 128, 0, s>>>(y, topk_idx, topk_w, pair_row, T, H, K, out_bf16, out_f32, tp, pv, rows_local, rank, residual);
 }
 
 // ---------------------------------------------------------------------------
