@@ -214,10 +214,10 @@ int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_b
     c->launches += 3;
   }
   launch_build_index(c->topk_idx, c->counts, T, E, K, n_nt1, n_nt2, c->offsets, c->tile_base, c->pair_row,
-                     c->row_token, c->row_slot, c->work1, c->work2, c->n_work, c->max_work1, c->max_work2, status, s);
+                     c->row_token, c->pair_slot, c->work1, c->work2, c->n_work, c->max_work1, c->max_work2, status, s);
   mark();
   if (flags & MOE_FWD_SIMT_GEMM) launch_gather_rows(t, c->row_token, c->offsets, E, c->xperm, H, P, s);
-  else launch_quantize_rows(t, c->row_token, c->row_slot, c->offsets + E, c->xq, c->sfa_x, H, P, s);
+  else launch_quantize_rows(t, c->pair_slot, T, K, c->xq, c->sfa_x, H, s);
   mark();
   const int add_b2 = c->cfg.tp_rank == 0 ? 1 : 0;
   if (flags & MOE_FWD_SIMT_GEMM) {
@@ -354,7 +354,7 @@ int moe_create(const moe_config *cfg, moe_handle *out) {
   if ((rc = dev_alloc(c, &c->offsets, (size_t)c->E + 1))) return rc;
   if ((rc = dev_alloc(c, &c->pair_row, T * c->K))) return rc;
   if ((rc = dev_alloc(c, &c->row_token, P))) return rc;
-  if ((rc = dev_alloc(c, &c->row_slot, P))) return rc;
+  if ((rc = dev_alloc(c, &c->pair_slot, P))) return rc;
   if ((rc = dev_alloc(c, &c->xperm, P * c->H))) return rc;
   if ((rc = dev_alloc(c, &c->hbuf, P * c->Kw))) return rc;
   if ((rc = dev_alloc(c, &c->ybuf, P * c->H))) return rc;
@@ -438,7 +438,7 @@ int moe_destroy(moe_handle c) {
   for (cudaEvent_t e : c->prof_events) cudaEventDestroy(e);
   for (cudaEvent_t e : c->prof_pool) cudaEventDestroy(e);
   cudaFree(c->t_in); cudaFree(c->t_norm); cudaFree(c->logits); cudaFree(c->router_part); cudaFree(c->topk_idx); cudaFree(c->topk_w); cudaFree(c->counts);
-  cudaFree(c->offsets); cudaFree(c->pair_row); cudaFree(c->row_token); cudaFree(c->row_slot); cudaFree(c->xperm); cudaFree(c->hbuf);
+  cudaFree(c->offsets); cudaFree(c->pair_row); cudaFree(c->row_token); cudaFree(c->pair_slot); cudaFree(c->xperm); cudaFree(c->hbuf);
   cudaFree(c->ybuf); cudaFree(c->out_f32); cudaFree(c->out_bf16); cudaFree(c->work1); cudaFree(c->work2);
   cudaFree(c->n_work); cudaFree(c->status);
   cudaFree(c->xq); cudaFree(c->hq); cudaFree(c->sfa_x); cudaFree(c->sfa_h); cudaFree(c->tile_base);

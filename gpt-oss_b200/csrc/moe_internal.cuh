@@ -144,7 +144,7 @@ struct moe_ctx {
   int *offsets = nullptr;           // d_expert_offsets    [E+1]
   int *pair_row = nullptr;          // local_ids_g         [max_rows, K]
   int *row_token = nullptr;         // expert_row_token_g  [max_pairs]
-  int *row_slot = nullptr;          // row of the token's high term in xq [max_pairs]
+  int *pair_slot = nullptr;         // row of the high term of (token, k) in xq [max_rows, K]
   __half *xperm = nullptr;          // expert_input_buffer [max_pairs, H]   fp16 (validation GEMM only)
   __half *hbuf = nullptr;           // gate_up             [max_pairs, Dl]  fp16 (validation GEMM only)
   uint8_t *xq = nullptr;            // expert_input_buffer as e4m3 high/low rows, [max_tiles][k slices][128 rows][128 B]
@@ -230,11 +230,11 @@ void launch_topk_softmax(float *logits, const float *partial, int splits, const 
                          int row_offset = 0);
 void launch_count_experts(const int *idx, int n, int E, int *counts, cudaStream_t s);
 void launch_build_index(const int *topk_idx, const int *counts, int T, int E, int K, int n_ntiles1, int n_ntiles2,
-                        int *offsets, int *tile_base, int *pair_row, int *row_token, int *row_slot, WorkItem *work1,
+                        int *offsets, int *tile_base, int *pair_row, int *row_token, int *pair_slot, WorkItem *work1,
                         WorkItem *work2, int *n_work, int max_work1, int max_work2, unsigned int *status,
                         cudaStream_t s);
-void launch_quantize_rows(const __nv_bfloat16 *t, const int *row_token, const int *row_slot, const int *n_rows_dev,
-                          uint8_t *xq, uint8_t *sfa, int H, int n_rows, cudaStream_t s);
+void launch_quantize_rows(const __nv_bfloat16 *t, const int *pair_slot, int T, int K, uint8_t *xq, uint8_t *sfa, int H,
+                          cudaStream_t s);
 int quantize_rows_max_hidden();
 void launch_gather_rows(const __nv_bfloat16 *t, const int *row_token, const int *offsets, int E, __half *xperm,
                         int H, int max_pairs, cudaStream_t s);

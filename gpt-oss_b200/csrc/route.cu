@@ -104,7 +104,7 @@ void launch_topk_softmax(float *logits, const float *partial, int splits, const 
 __global__ void __launch_bounds__(256)
 build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ counts, int T, int E, int K,
                    int n_ntiles1, int n_ntiles2, int *__restrict__ offsets, int *__restrict__ tile_base,
-                   int *__restrict__ pair_row, int *__restrict__ row_token, int *__restrict__ row_slot,
+                   int *__restrict__ pair_row, int *__restrict__ row_token, int *__restrict__ pair_slot,
                    WorkItem *__restrict__ work1,
                    WorkItem *__restrict__ work2, int *__restrict__ n_work, int max_work1, int max_work2,
                    unsigned int *status) {
@@ -178,7 +178,7 @@ build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ cou
         const int r = off + pos;
         row_token[r] = t;
         // where the row's high term goes in the quantised activations: token tile, then 2 rows per token
-        row_slot[r] = (tiles_before + pos / kTokTile) * kTileM + 2 * (pos % kTokTile);
+        pair_slot[static_cast<size_t>(t) * K + hit] = (tiles_before + pos / kTokTile) * kTileM + 2 * (pos % kTokTile);
         pair_row[static_cast<size_t>(t) * K + hit] = r;
       } else {
         atomicOr(status, ST_BAD_INDEX);
@@ -219,11 +219,11 @@ build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ cou
 }
 
 void launch_build_index(const int *topk_idx, const int *counts, int T, int E, int K, int n_ntiles1, int n_ntiles2,
-                        int *offsets, int *tile_base, int *pair_row, int *row_token, int *row_slot,
+                        int *offsets, int *tile_base, int *pair_row, int *row_token, int *pair_slot,
                         WorkItem *work1, WorkItem *work2, int *n_work, int max_work1, int max_work2,
                         unsigned int *status, cudaStream_t s) {
   build_index_kernel<<<E, 256, 0, s>>>(topk_idx, counts, T, E, K, n_ntiles1, n_ntiles2, offsets, tile_base,
-                                       pair_row, row_token, row_slot, work1, work2, n_work, max_work1, max_work2, status);
+                                       pair_row, row_token, pair_slot, work1, work2, n_work, max_work1, max_work2, status);
 }
 
 // ---------------------------------------------------------------------------
@@ -239,31 +239,37 @@ void launch_build_index(const int *topk_idx, const int *counts, int T, int E, in
 // into the tile's 512-byte scale atom, byte (r%32)*16 + (r/32)*4 + kb for row r
 // and every k block kb (the scale is per row, so the four bytes are equal).
 // ---------------------------------------------------------------------------
-constexpr int kQrWarps = 4;   // a warp per row: the row (kQrVec x 16 bytes per lane) stays in its registers
+// The two rows depend on the token only, not on the expert, so a warp quantises one TOKEN (its row stays in
+// the warp's registers: kQrVec x 32 bytes per lane) and stores the result once per selected expert, at the
+// tile rows build_index_kernel assigned to the (token, expert) pairs.
+constexpr int kQrWarps = 4;
 
-template <int kQrVec>         // 12: rows of up to 3072 elements, 16: up to 4096
+template <int kQrVec>         // 6: rows of up to 3072 elements, 8: up to 4096
 __global__ void __launch_bounds__(kQrWarps * 32)
-quantize_rows_kernel(const __nv_bfloat16 *__restrict__ t, const int *__restrict__ row_token,
-                     const int *__restrict__ row_slot, const int *__restrict__ n_rows,
+quantize_rows_kernel(const __nv_bfloat16 *__restrict__ t, const int *__restrict__ pair_slot, int T, int K,
                      uint8_t *__restrict__ xq, uint8_t *__restrict__ sfa, int H) {
   const int lane = threadIdx.x & 31;
-  const int r = blockIdx.x * kQrWarps + (threadIdx.x >> 5);
-  if (r >= *n_rows) return;   // whole warps leave: no block-wide barrier below
-  const int tok = row_token[r], slot = row_slot[r];
-  const int tile = slot / kTileM, i2 = slot % kTileM;   // i2 = 2 * (token's place in the tile)
+  const int tok = blockIdx.x * kQrWarps + (threadIdx.x >> 5);
+  if (tok >= T) return;   // whole warps leave: no block-wide barrier below
+  int slot[kMaxTopK];
+#pragma unroll
+  for (int k = 0; k < kMaxTopK; ++k) slot[k] = k < K ? pair_slot[static_cast<size_t>(tok) * K + k] : -1;
   const uint4 *src = reinterpret_cast<const uint4 *>(t + static_cast<size_t>(tok) * H);
-  const int nvec = H / 8;
-  uint4 v[kQrVec];
+  const int ngrp = H / 16;    // a lane takes groups of 16 elements: 32 bytes in, 16 + 16 bytes out
+  uint4 v[kQrVec][2];
   float amax = 0.f;
 #pragma unroll
   for (int u = 0; u < kQrVec; ++u) {
-    const int c = lane + u * 32;
-    v[u] = c < nvec ? __ldg(src + c) : make_uint4(0u, 0u, 0u, 0u);
-    const uint32_t in[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+    const int g = lane + u * 32;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      amax = fmaxf(amax, fabsf(__uint_as_float(in[j] << 16)));
-      amax = fmaxf(amax, fabsf(__uint_as_float(in[j] & 0xffff0000u)));
+    for (int h = 0; h < 2; ++h) {
+      v[u][h] = g < ngrp ? __ldg(src + 2 * g + h) : make_uint4(0u, 0u, 0u, 0u);
+      const uint32_t in[4] = {v[u][h].x, v[u][h].y, v[u][h].z, v[u][h].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        amax = fmaxf(amax, fabsf(__uint_as_float(in[j] << 16)));
+        amax = fmaxf(amax, fabsf(__uint_as_float(in[j] & 0xffff0000u)));
+      }
     }
   }
 #pragma unroll
@@ -272,57 +278,70 @@ quantize_rows_kernel(const __nv_bfloat16 *__restrict__ t, const int *__restrict_
   int e = static_cast<int>((__float_as_uint(amax) >> 23) & 0xffu) - 127 - 7;
   e = max(-120, min(e, 120));
   const float inv = __uint_as_float(static_cast<uint32_t>(127 - e) << 23);  // 2^-e
-  // activation tiles: [tile][k slice][128 rows][128 bytes]; 8 elements never straddle a slice
+  // activation tiles: [tile][k slice][128 rows][128 bytes]; 16 elements never straddle a slice
   const int n_kc = (H + kChunkK - 1) / kChunkK;
-  uint8_t *tile_hi = xq + (static_cast<size_t>(tile) * n_kc * kTileM + i2) * kChunkK;
 #pragma unroll
   for (int u = 0; u < kQrVec; ++u) {
-    const int c = lane + u * 32;
-    if (c >= nvec) break;
-    const uint32_t in[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-    float f[8];
+    const int g = lane + u * 32;
+    if (g >= ngrp) break;
+    uint32_t h8[4], l8[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      f[2 * j] = __uint_as_float(in[j] << 16) * inv;
-      f[2 * j + 1] = __uint_as_float(in[j] & 0xffff0000u) * inv;
-    }
-    uint32_t h8[2], l8[2];
-#pragma unroll
-    for (int g = 0; g < 2; ++g) {
-      const uint32_t a = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * g], f[4 * g + 1]), __NV_SATFINITE, __NV_E4M3);
-      const uint32_t b = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * g + 2], f[4 * g + 3]), __NV_SATFINITE, __NV_E4M3);
-      h8[g] = a | (b << 16);
-      float rs[4];
+    for (int h = 0; h < 2; ++h) {
+      const uint32_t in[4] = {v[u][h].x, v[u][h].y, v[u][h].z, v[u][h].w};
+      float f[8];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const __half_raw hr = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>((h8[g] >> (8 * j)) & 0xffu), __NV_E4M3);
-        rs[j] = (f[4 * g + j] - __half2float(*reinterpret_cast<const __half *>(&hr))) * 16.0f;
+        f[2 * j] = __uint_as_float(in[j] << 16) * inv;
+        f[2 * j + 1] = __uint_as_float(in[j] & 0xffff0000u) * inv;
       }
-      const uint32_t c2 = __nv_cvt_float2_to_fp8x2(make_float2(rs[0], rs[1]), __NV_SATFINITE, __NV_E4M3);
-      const uint32_t d2 = __nv_cvt_float2_to_fp8x2(make_float2(rs[2], rs[3]), __NV_SATFINITE, __NV_E4M3);
-      l8[g] = c2 | (d2 << 16);
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const uint32_t a = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * q], f[4 * q + 1]), __NV_SATFINITE, __NV_E4M3);
+        const uint32_t b = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * q + 2], f[4 * q + 3]), __NV_SATFINITE, __NV_E4M3);
+        const uint32_t hi = a | (b << 16);
+        h8[2 * h + q] = hi;
+        float rs[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const __half_raw hr = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>((hi >> (8 * j)) & 0xffu), __NV_E4M3);
+          rs[j] = (f[4 * q + j] - __half2float(*reinterpret_cast<const __half *>(&hr))) * 16.0f;
+        }
+        const uint32_t c2 = __nv_cvt_float2_to_fp8x2(make_float2(rs[0], rs[1]), __NV_SATFINITE, __NV_E4M3);
+        const uint32_t d2 = __nv_cvt_float2_to_fp8x2(make_float2(rs[2], rs[3]), __NV_SATFINITE, __NV_E4M3);
+        l8[2 * h + q] = c2 | (d2 << 16);
+      }
     }
-    uint8_t *dst = tile_hi + static_cast<size_t>(c >> 4) * (kTileM * kChunkK) + (c & 15) * 8;  // slice c/16, byte 8*(c%16)
-    *reinterpret_cast<uint2 *>(dst) = make_uint2(h8[0], h8[1]);
-    *reinterpret_cast<uint2 *>(dst + kChunkK) = make_uint2(l8[0], l8[1]);                      // the low row follows
+    const size_t in_tile = static_cast<size_t>(g >> 3) * (kTileM * kChunkK) + (g & 7) * 16;  // slice g/8, byte 16*(g%8)
+#pragma unroll
+    for (int k = 0; k < kMaxTopK; ++k) {
+      if (slot[k] < 0) continue;
+      const int tile = slot[k] / kTileM, i2 = slot[k] % kTileM;   // i2 = 2 * (token's place in the tile)
+      uint8_t *dst = xq + (static_cast<size_t>(tile) * n_kc * kTileM + i2) * kChunkK + in_tile;
+      *reinterpret_cast<uint4 *>(dst) = make_uint4(h8[0], h8[1], h8[2], h8[3]);
+      *reinterpret_cast<uint4 *>(dst + kChunkK) = make_uint4(l8[0], l8[1], l8[2], l8[3]);   // the low row follows
+    }
   }
   if (lane < 2) {
-    const int rr = i2 + lane;  // row inside the tile: even = high, odd = low
     const uint32_t byte = static_cast<uint32_t>(127 + e - 4 * lane);
-    uint8_t *atom = sfa + static_cast<size_t>(tile) * kSfAtomBytes;
-    *reinterpret_cast<uint32_t *>(atom + (rr % 32) * 16 + (rr / 32) * 4) = byte * 0x01010101u;
+#pragma unroll
+    for (int k = 0; k < kMaxTopK; ++k) {
+      if (slot[k] < 0) continue;
+      const int tile = slot[k] / kTileM, rr = slot[k] % kTileM + lane;  // row inside the tile: even = high, odd = low
+      uint8_t *atom = sfa + static_cast<size_t>(tile) * kSfAtomBytes;
+      *reinterpret_cast<uint32_t *>(atom + (rr % 32) * 16 + (rr / 32) * 4) = byte * 0x01010101u;
+    }
   }
 }
 
-int quantize_rows_max_hidden() { return 32 * 16 * 8; }
+int quantize_rows_max_hidden() { return 32 * 8 * 16; }
 
-void launch_quantize_rows(const __nv_bfloat16 *t, const int *row_token, const int *row_slot, const int *n_rows_dev,
-                          uint8_t *xq, uint8_t *sfa, int H, int n_rows, cudaStream_t s) {
-  const int blocks = (n_rows + kQrWarps - 1) / kQrWarps;
-  if (H <= 32 * 12 * 8)
-    quantize_rows_kernel<12><<<blocks, kQrWarps * 32, 0, s>>>(t, row_token, row_slot, n_rows_dev, xq, sfa, H);
+void launch_quantize_rows(const __nv_bfloat16 *t, const int *pair_slot, int T, int K, uint8_t *xq, uint8_t *sfa, int H,
+                          cudaStream_t s) {
+  const int blocks = (T + kQrWarps - 1) / kQrWarps;
+  if (H <= 32 * 6 * 16)
+    quantize_rows_kernel<6><<<blocks, kQrWarps * 32, 0, s>>>(t, pair_slot, T, K, xq, sfa, H);
   else
-    quantize_rows_kernel<16><<<blocks, kQrWarps * 32, 0, s>>>(t, row_token, row_slot, n_rows_dev, xq, sfa, H);
+    quantize_rows_kernel<8><<<blocks, kQrWarps * 32, 0, s>>>(t, pair_slot, T, K, xq, sfa, H);
 }
 
 // ---------------------------------------------------------------------------
