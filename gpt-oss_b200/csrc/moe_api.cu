@@ -207,14 +207,19 @@ int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_b
     }
     CU_TRY(c, cudaEventRecord(c->ev_join, c->aux_stream));
     if (int rc = route_rows(t_local, tp_rows_local)) return rc;
-    CU_TRY(c, cudaStreamWaitEvent(s, c->ev_join, 0));
-    launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, 0, c->tp_epoch, status, s);
+    // the selections (a few kilobytes per rank) are exchanged first: histogram and index are built while
+    // the rows of the all-gather are still crossing the links
+    launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, kTpPhaseSelection, c->tp_epoch, status, s);
     launch_count_experts(c->topk_idx, T * K, E, c->counts, s);
     mark();
-    c->launches += 3;
+    c->launches += 4;
   }
   launch_build_index(c->topk_idx, c->counts, T, E, K, n_nt1, n_nt2, c->offsets, c->tile_base, c->pair_row,
                      c->row_token, c->pair_slot, c->work1, c->work2, c->n_work, c->max_work1, c->max_work2, status, s);
+  if (tpcall) {   // now the gathered rows: this rank's push is complete (side stream), then every peer's
+    CU_TRY(c, cudaStreamWaitEvent(s, c->ev_join, 0));
+    launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, kTpPhaseGather, c->tp_epoch, status, s);
+  }
   mark();
   if (flags & MOE_FWD_SIMT_GEMM) launch_gather_rows(t, c->row_token, c->offsets, E, c->xperm, H, P, s);
   else launch_quantize_rows(t, c->pair_slot, T, K, c->xq, c->sfa_x, H, s);
@@ -255,7 +260,7 @@ int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_b
     launch_combine(c->ybuf, c->topk_idx, c->topk_w, c->pair_row, T, H, K, c->tp_partial,
                    (c->cfg.flags & MOE_CFG_KEEP_F32_OUT) ? c->out_f32 : nullptr, s, tp, &c->peers, tp_rows_local, rank);
     ++c->tp_epoch_rs;
-    launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, 1, c->tp_epoch_rs, status, s);
+    launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, kTpPhaseScatter, c->tp_epoch_rs, status, s);
     launch_tp_sum_slots(c->tp_partial, tp, tp_rows_local, H, out_dev, c->sm_count, s, residual);
     mark();
     c->launches += 2;
@@ -362,8 +367,8 @@ int moe_create(const moe_config *cfg, moe_handle *out) {
   if ((rc = dev_alloc(c, &c->out_bf16, T * c->H))) return rc;
   // symmetric buffers of the TP group; this rank's own entries are known now
   if ((rc = dev_alloc(c, &c->tp_partial, T * c->H))) return rc;
-  if ((rc = dev_alloc(c, &c->tp_flags, static_cast<size_t>(2) * kMaxTp))) return rc;
-  CU_TRY(c, cudaMemset(c->tp_flags, 0, 2 * kMaxTp * sizeof(uint32_t)));
+  if ((rc = dev_alloc(c, &c->tp_flags, static_cast<size_t>(kTpPhases) * kMaxTp))) return rc;
+  CU_TRY(c, cudaMemset(c->tp_flags, 0, kTpPhases * kMaxTp * sizeof(uint32_t)));
   if (cfg->tp_size > kMaxTp) return fail(c, MOE_ERR_INVALID, "tp_size %d above %d", cfg->tp_size, kMaxTp);
   c->peers.gather[cfg->tp_rank] = c->t_in;
   c->peers.partial[cfg->tp_rank] = c->tp_partial;

@@ -51,11 +51,14 @@ constexpr int kMaxTp = 8;  // MAX_TP of getp-csrc/nccl.hpp:6
 struct TpPeers {
   void *gather[kMaxTp];       // bf16 [max_rows, H]: all-gather destination (gather_x_g)
   void *partial[kMaxTp];      // bf16 [max_rows, H]: this rank's partial block output (e_agg_g)
-  uint32_t *flags[kMaxTp];    // [2 phases][kMaxTp] epoch words
+  uint32_t *flags[kMaxTp];    // [kTpPhases][kMaxTp] epoch words
   void *topk_idx[kMaxTp];     // i32 [max_rows, K]: every rank routes its own rows and writes them to all (topk_i_g)
   void *topk_w[kMaxTp];       // f32 [max_rows, K]                                                  (topk_v_g)
 };
 constexpr int kTpBufs = 5;
+// Hand-shakes of a tensor-parallel call, each with its own row of epoch words: the gathered rows are in
+// place, the partial outputs are in place, the expert selections are in place.
+enum { kTpPhaseGather = 0, kTpPhaseScatter = 1, kTpPhaseSelection = 2, kTpPhases = 3 };
 
 // One call in flight through moe_forward_host_submit: its own input and output staging, so that the copies of
 // neighbouring calls overlap the block of this one.
@@ -166,7 +169,7 @@ struct moe_ctx {
   long long launches = 0;
   moe::TpPeers peers = {};          // TP group view; own entries are set at creation
   __nv_bfloat16 *tp_partial = nullptr;  // this rank's bf16 partial output [max_rows, H]
-  uint32_t *tp_flags = nullptr;     // [2][kMaxTp], written by the peers
+  uint32_t *tp_flags = nullptr;     // [kTpPhases][kMaxTp], written by the peers
   uint64_t tp_attached = 0;         // bit (kTpBufs*r + which) set once rank r's buffer `which` is known
   moe::HostSlot host_slots[moe::kHostSlots];
   cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;

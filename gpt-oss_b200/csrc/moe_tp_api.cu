@@ -119,7 +119,7 @@ int moe_tp_allgather(moe_handle c, const void *src, int rows_local, void *stream
   const int tp = c->cfg.tp_size, rank = c->cfg.tp_rank;
   ++c->tp_epoch;
   launch_tp_allgather_push(static_cast<const __nv_bfloat16 *>(src), rows_local, c->H, c->peers, tp, rank, c->sm_count, s);
-  launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, 0, c->tp_epoch, c->status, s);
+  launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, kTpPhaseGather, c->tp_epoch, c->status, s);
   c->launches += 2;
   if (cudaGetLastError() != cudaSuccess) return tp_fail(c, MOE_ERR_CUDA, "moe_tp_allgather: launch failed");
   return MOE_OK;
@@ -132,7 +132,7 @@ int moe_tp_reduce_scatter(moe_handle c, int rows_local, void *out_local, void *s
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int tp = c->cfg.tp_size, rank = c->cfg.tp_rank;
   ++c->tp_epoch_rs;  // every rank calls in lock-step, so the counters agree across the group
-  launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, 1, c->tp_epoch_rs, c->status, s);
+  launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, kTpPhaseScatter, c->tp_epoch_rs, c->status, s);
   launch_tp_reduce_scatter_pull(c->peers, tp, rank, rows_local, c->H, static_cast<__nv_bfloat16 *>(out_local),
                                 c->sm_count, s);
   c->launches += 2;
@@ -153,11 +153,11 @@ int moe_tp_allreduce(moe_handle c, void *buf_dev, size_t n_elems, void *stream) 
   // 1. every rank has finished reading the partial buffers of the previous collective; 2. this rank's values are
   // in its partial buffer; 3. every rank's values are in place; 4. sum all ranks' buffers in rank order.
   ++c->tp_epoch;
-  launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, 0, c->tp_epoch, c->status, s);
+  launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, kTpPhaseGather, c->tp_epoch, c->status, s);
   if (cudaMemcpyAsync(c->tp_partial, buf_dev, n_elems * 2, cudaMemcpyDeviceToDevice, s) != cudaSuccess)
     return tp_fail(c, MOE_ERR_CUDA, "moe_tp_allreduce: staging copy failed");
   ++c->tp_epoch_rs;
-  launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, 1, c->tp_epoch_rs, c->status, s);
+  launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, kTpPhaseScatter, c->tp_epoch_rs, c->status, s);
   launch_tp_sum_all(c->peers, tp, n_elems, static_cast<__nv_bfloat16 *>(buf_dev), c->sm_count, s);
   c->launches += 3;
   if (cudaGetLastError() != cudaSuccess) return tp_fail(c, MOE_ERR_CUDA, "moe_tp_allreduce: launch failed");

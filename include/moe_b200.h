@@ -172,7 +172,7 @@ int moe_route_topk(moe_handle h, const float *logits_dev, int rows, int *idx_dev
 enum {
   MOE_TP_BUF_GATHER = 0,  /* bf16 [max_rows, H]  all-gather destination        (gather_x_g) */
   MOE_TP_BUF_PARTIAL = 1, /* bf16 [max_rows, H]  this rank's partial output    (e_agg_g)    */
-  MOE_TP_BUF_FLAGS = 2,   /* u32  [2][8]         arrival epochs written by the peers        */
+  MOE_TP_BUF_FLAGS = 2,   /* u32  [3][8]         arrival epochs written by the peers        */
   MOE_TP_BUF_TOPK_IDX = 3,/* i32  [max_rows, K]  expert choice of every row of the union    (topk_i_g)  */
   MOE_TP_BUF_TOPK_W = 4,  /* f32  [max_rows, K]  routing weights of every row of the union  (topk_v_g)  */
   MOE_TP_N_BUFS = 5
