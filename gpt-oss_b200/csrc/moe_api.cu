@@ -191,25 +191,32 @@ int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_b
     if (int rc = route_rows(t, T)) return rc;
     mark();
   } else {
-    // all-gather push of this rank's rows on the side stream, beside the routing of the same rows
+    // The all-gather push runs on the side stream in two parts.  The first starts at once, beside the
+    // routing of the same rows; the router's few peer stores (the selections, written to every rank) queue
+    // behind it on the links, which is why it is only a part.  Once the selections are exchanged the second
+    // part goes out, while this stream builds histogram and index from them.
     ++c->tp_epoch;
+    const int part_a = tp_rows_local >= 256 ? (tp_rows_local * 2 / 5 + 7) / 8 * 8 : tp_rows_local;
+    auto push_rows = [&](int row0, int n) {
+      if (norm_gain != nullptr) launch_tp_rmsnorm_push(residual, norm_gain, tp_rows_local, H, c->peers, tp, rank, c->aux_stream, row0, n);
+      else launch_tp_allgather_push(t_local, tp_rows_local, H, c->peers, tp, rank, c->aux_stream, row0, n);
+    };
     CU_TRY(c, cudaEventRecord(c->ev_fork, s));
     CU_TRY(c, cudaStreamWaitEvent(c->aux_stream, c->ev_fork, 0));
-    if (norm_gain != nullptr) {
-      // moe_block: the push normalises the residual rows on the fly (side stream) while this stream
-      // normalises the same rows into t_norm for the router
-      launch_tp_rmsnorm_push(residual, norm_gain, tp_rows_local, H, c->peers, tp, rank, c->aux_stream);
+    push_rows(0, part_a);
+    if (norm_gain != nullptr) {   // moe_block: the rows the router reads are normalised here, the push normalises on the fly
       launch_rmsnorm_rows(residual, norm_gain, c->t_norm, tp_rows_local, H, s);
-      t_local = c->t_norm;
       c->launches += 1;
-    } else {
-      launch_tp_allgather_push(t_local, tp_rows_local, H, c->peers, tp, rank, c->sm_count, c->aux_stream);
+    }
+    if (int rc = route_rows(norm_gain != nullptr ? c->t_norm : t_local, tp_rows_local)) return rc;
+    launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, kTpPhaseSelection, c->tp_epoch, status, s);
+    if (part_a < tp_rows_local) {
+      CU_TRY(c, cudaEventRecord(c->ev_fork2, s));
+      CU_TRY(c, cudaStreamWaitEvent(c->aux_stream, c->ev_fork2, 0));
+      push_rows(part_a, tp_rows_local - part_a);
+      c->launches += 1;
     }
     CU_TRY(c, cudaEventRecord(c->ev_join, c->aux_stream));
-    if (int rc = route_rows(t_local, tp_rows_local)) return rc;
-    // the selections (a few kilobytes per rank) are exchanged first: histogram and index are built while
-    // the rows of the all-gather are still crossing the links
-    launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, kTpPhaseSelection, c->tp_epoch, status, s);
     launch_count_experts(c->topk_idx, T * K, E, c->counts, s);
     mark();
     c->launches += 4;
@@ -378,6 +385,7 @@ int moe_create(const moe_config *cfg, moe_handle *out) {
   c->tp_attached |= ((1ull << kTpBufs) - 1) << (kTpBufs * cfg->tp_rank);
   CU_TRY(c, cudaStreamCreateWithFlags(&c->aux_stream, cudaStreamNonBlocking));
   CU_TRY(c, cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming));
+  CU_TRY(c, cudaEventCreateWithFlags(&c->ev_fork2, cudaEventDisableTiming));
   CU_TRY(c, cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming));
   const int n_nt1 = (c->R1 + kTileN - 1) / kTileN, n_nt2 = (c->H + kTileN - 1) / kTileN;
   c->max_tiles = c->max_pairs / kTokTile + c->E + 1;
@@ -437,6 +445,7 @@ int moe_destroy(moe_handle c) {
       if (e) cudaEventDestroy(e);
   }
   if (c->ev_fork) cudaEventDestroy(c->ev_fork);
+  if (c->ev_fork2) cudaEventDestroy(c->ev_fork2);
   if (c->ev_join) cudaEventDestroy(c->ev_join);
   cudaFree(c->tp_partial); cudaFree(c->tp_flags);
   for (auto &w : c->layers) free_layer(w);

@@ -175,7 +175,7 @@ struct moe_ctx {
   cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
   long long host_submitted = 0;
   cudaStream_t aux_stream = nullptr;  // the all-gather push runs beside the router
-  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+  cudaEvent_t ev_fork = nullptr, ev_fork2 = nullptr, ev_join = nullptr;
   uint32_t tp_epoch = 0, tp_epoch_rs = 0;  // all-gather / reduce-scatter call counters
   std::vector<void *> ipc_opened;   // mappings to close at destroy
   bool profiling = false;
@@ -256,10 +256,11 @@ void launch_expert_gemm_mlp2(const CUtensorMap &tm_w, const CUtensorMap &tm_x, c
                              cudaStream_t s);
 
 // tp_collectives.cu
+// Both pushes send rows [row0, row0 + n_rows) of this rank's rows_local rows (n_rows < 0: all of them).
 void launch_tp_allgather_push(const __nv_bfloat16 *src, int rows_local, int H, const TpPeers &peers, int tp, int rank,
-                              int sm_count, cudaStream_t s);
+                              cudaStream_t s, int row0 = 0, int n_rows = -1);
 void launch_tp_rmsnorm_push(const __nv_bfloat16 *x, const __nv_bfloat16 *w, int rows_local, int H, const TpPeers &peers,
-                            int tp, int rank, cudaStream_t s);
+                            int tp, int rank, cudaStream_t s, int row0 = 0, int n_rows = -1);
 void launch_tp_signal_wait(const TpPeers &peers, uint32_t *my_flags, int tp, int rank, int phase, uint32_t epoch,
                            unsigned int *status, cudaStream_t s);
 void launch_tp_sum_slots(const __nv_bfloat16 *landing, int tp, int rows_local, int H, __nv_bfloat16 *out, int sm_count,

@@ -118,7 +118,7 @@ int moe_tp_allgather(moe_handle c, const void *src, int rows_local, void *stream
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int tp = c->cfg.tp_size, rank = c->cfg.tp_rank;
   ++c->tp_epoch;
-  launch_tp_allgather_push(static_cast<const __nv_bfloat16 *>(src), rows_local, c->H, c->peers, tp, rank, c->sm_count, s);
+  launch_tp_allgather_push(static_cast<const __nv_bfloat16 *>(src), rows_local, c->H, c->peers, tp, rank, s);
   launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, kTpPhaseGather, c->tp_epoch, c->status, s);
   c->launches += 2;
   if (cudaGetLastError() != cudaSuccess) return tp_fail(c, MOE_ERR_CUDA, "moe_tp_allgather: launch failed");

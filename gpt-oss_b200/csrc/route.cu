@@ -101,16 +101,17 @@ void launch_topk_softmax(float *logits, const float *partial, int splits, const 
 // route_build_index_kernel_bf16wts (kernels/moe.hpp:1173-1270): rows of one
 // expert are in ascending token order.
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ counts, int T, int E, int K,
                    int n_ntiles1, int n_ntiles2, int *__restrict__ offsets, int *__restrict__ tile_base,
                    int *__restrict__ pair_row, int *__restrict__ row_token, int *__restrict__ pair_slot,
                    WorkItem *__restrict__ work1,
                    WorkItem *__restrict__ work2, int *__restrict__ n_work, int max_work1, int max_work2,
                    unsigned int *status) {
-  __shared__ int s_red[2][8];
-  __shared__ int s_warp[8];
+  __shared__ int s_red[2][32];
+  __shared__ int s_warp[32];
   const int e = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_warps = blockDim.x >> 5;   // 8, or 32 for batches whose selections 8 warps cannot hold in registers
 
   // exclusive prefix over experts below e: rows and token tiles
   int my_rows = 0, my_tiles = 0;
@@ -127,8 +128,7 @@ build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ cou
   if (lane == 0) { s_red[0][warp] = my_rows; s_red[1][warp] = my_tiles; }
   __syncthreads();
   int off = 0, tiles_before = 0;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) { off += s_red[0][i]; tiles_before += s_red[1][i]; }
+  for (int i = 0; i < n_warps; ++i) { off += s_red[0][i]; tiles_before += s_red[1][i]; }
   const int cnt = counts[e];
   const int ntt = (cnt + kTokTile - 1) / kTokTile;  // token tiles of this expert (rows e's tiles, in order)
   if (tid == 0) {
@@ -138,9 +138,9 @@ build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ cou
   }
 
   // Stable compaction in ascending token order.  Warp w owns the contiguous token range [w*per, (w+1)*per):
-  // a first walk counts the range's hits with ballots, one block-wide barrier turns the eight counts into
+  // a first walk counts the range's hits with ballots, one block-wide barrier turns the warps' counts into
   // starting positions, a second walk writes the rows.  No barrier per step.
-  const int per = ((T + 7) / 8 + 31) / 32 * 32;       // tokens per warp, whole ballot steps
+  const int per = ((T + n_warps - 1) / n_warps + 31) / 32 * 32;       // tokens per warp, whole ballot steps
   const int t_begin = warp * per, t_end = min(T, t_begin + per);
   auto hit_of = [&](int t) -> int {
     if (t >= t_end) return -1;
@@ -152,7 +152,7 @@ build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ cou
       if (topk_idx[static_cast<size_t>(t) * K + k] == e) return k;
     return -1;
   };
-  // the first kCached ballot steps of the range (all of it up to 2048 tokens) are loaded at once and kept
+  // the first kCached ballot steps of the range (all of it up to 256 tokens per warp) are loaded at once and kept
   constexpr int kCached = 8;
   int cached[kCached];
 #pragma unroll
@@ -165,8 +165,7 @@ build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ cou
   if (lane == 0) s_warp[warp] = mine;
   __syncthreads();
   int before = 0, total_hits = 0;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
+  for (int i = 0; i < n_warps; ++i) {
     before += i < warp ? s_warp[i] : 0;
     total_hits += s_warp[i];
   }
@@ -222,7 +221,7 @@ void launch_build_index(const int *topk_idx, const int *counts, int T, int E, in
                         int *offsets, int *tile_base, int *pair_row, int *row_token, int *pair_slot,
                         WorkItem *work1, WorkItem *work2, int *n_work, int max_work1, int max_work2,
                         unsigned int *status, cudaStream_t s) {
-  build_index_kernel<<<E, 256, 0, s>>>(topk_idx, counts, T, E, K, n_ntiles1, n_ntiles2, offsets, tile_base,
+  build_index_kernel<<<E, T > 2048 ? 1024 : 256, 0, s>>>(topk_idx, counts, T, E, K, n_ntiles1, n_ntiles2, offsets, tile_base,
                                        pair_row, row_token, pair_slot, work1, work2, n_work, max_work1, max_work2, status);
 }
 

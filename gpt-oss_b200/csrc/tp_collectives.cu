@@ -20,6 +20,8 @@
 
 namespace moe {
 
+constexpr int kPushBlocks = 32;
+
 __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -32,10 +34,17 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
 // Every rank's rows [rows_local, H] -> slot `rank` of the gather buffer of every rank of the group.
 __global__ void __launch_bounds__(256)
 tp_allgather_push_kernel(const uint4 *__restrict__ src, size_t n_vec, TpPeers peers, int tp, size_t slot_vec) {
+  // four vectors per thread and step: the loads are in flight together, the stores are posted
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
-  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
-    const uint4 v = __ldg(src + i);
-    for (int r = 0; r < tp; ++r) reinterpret_cast<uint4 *>(peers.gather[r])[slot_vec + i] = v;
+  for (size_t i0 = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < n_vec; i0 += 4 * stride) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (i0 + u * stride < n_vec) v[u] = __ldg(src + i0 + u * stride);
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (i0 + u * stride < n_vec)
+        for (int r = 0; r < tp; ++r) reinterpret_cast<uint4 *>(peers.gather[r])[slot_vec + i0 + u * stride] = v[u];
   }
 }
 
@@ -183,16 +192,24 @@ void launch_tp_sum_slots(const __nv_bfloat16 *landing, int tp, int rows_local, i
 }
 
 void launch_tp_allgather_push(const __nv_bfloat16 *src, int rows_local, int H, const TpPeers &peers, int tp, int rank,
-                              int sm_count, cudaStream_t s) {
-  const size_t n_vec = static_cast<size_t>(rows_local) * H / 8;
-  const int blocks = static_cast<int>(std::min<size_t>((n_vec + 255) / 256, static_cast<size_t>(sm_count) * 4));
-  tp_allgather_push_kernel<<<std::max(blocks, 1), 256, 0, s>>>(reinterpret_cast<const uint4 *>(src), n_vec, peers, tp,
-                                                              static_cast<size_t>(rank) * n_vec);
+                              cudaStream_t s, int row0, int n_rows) {
+  // A few dozen blocks keep the links full (the stores are posted); the rest of the GPU stays free for the
+  // kernels of the other stream that run beside the push.
+  if (n_rows < 0) n_rows = rows_local - row0;
+  if (n_rows <= 0) return;
+  const size_t row_vec = static_cast<size_t>(H) / 8, n_vec = static_cast<size_t>(n_rows) * row_vec;
+  const int blocks = static_cast<int>(std::min<size_t>((n_vec + 1023) / 1024, static_cast<size_t>(kPushBlocks)));
+  tp_allgather_push_kernel<<<std::max(blocks, 1), 256, 0, s>>>(
+      reinterpret_cast<const uint4 *>(src) + static_cast<size_t>(row0) * row_vec, n_vec, peers, tp,
+      (static_cast<size_t>(rank) * rows_local + row0) * row_vec);
 }
 
 void launch_tp_rmsnorm_push(const __nv_bfloat16 *x, const __nv_bfloat16 *w, int rows_local, int H, const TpPeers &peers,
-                            int tp, int rank, cudaStream_t s) {
-  tp_rmsnorm_push_kernel<<<rows_local, 256, 0, s>>>(x, w, H, peers, tp, static_cast<size_t>(rank) * rows_local);
+                            int tp, int rank, cudaStream_t s, int row0, int n_rows) {
+  if (n_rows < 0) n_rows = rows_local - row0;
+  if (n_rows <= 0) return;
+  tp_rmsnorm_push_kernel<<<n_rows, 256, 0, s>>>(x + static_cast<size_t>(row0) * H, w, H, peers, tp,
+                                                static_cast<size_t>(rank) * rows_local + row0);
 }
 
 void launch_tp_signal_wait(const TpPeers &peers, uint32_t *my_flags, int tp, int rank, int phase, uint32_t epoch,
