@@ -26,6 +26,7 @@ CFG_KEEP_F32_OUT = 1
 FWD_SIMT_GEMM = 1
 FWD_PARTIAL_F32 = 2
 FWD_SPLIT_ROUTER = 4
+FWD_SPLIT_MLP = 8
 
 DBG_LOGITS, DBG_TOPK_IDX, DBG_TOPK_W, DBG_COUNTS, DBG_OFFSETS, DBG_PAIR_ROW, DBG_ROW_TOKEN, DBG_OUT_F32, \
     DBG_STATUS, DBG_HBUF, DBG_YBUF, DBG_GATHER, DBG_TNORM, DBG_TP_PARTIAL = range(14)

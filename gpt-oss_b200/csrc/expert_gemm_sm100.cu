@@ -80,10 +80,24 @@ __device__ __forceinline__ float e4m3_to_float(uint32_t byte) {
   return __half2float(*reinterpret_cast<const __half *>(&h));
 }
 
-template <int MODE>  // 1 = MLP1 (bias + SwiGLU -> e4m3 high/low rows), 2 = MLP2 (bias -> fp16)
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const unsigned int *p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// One launch runs the phases [f.phase_begin, f.phase_end): phase 0 = MLP1 (bias + SwiGLU -> e4m3 high/low
+// rows, args pa), phase 1 = MLP2 (bias -> fp16, args pb).  Run together, the pipeline state (stage ring,
+// accumulator buffers, scale slots) simply carries over from the last MLP1 item of a CTA to its first MLP2
+// item: no drain, no second prologue, and CTAs that are out of MLP1 items start on MLP2 while the others
+// finish.  An MLP2 item reads the SwiGLU rows of its token tile, which the MLP1 items of that tile (on any
+// SM) have written: every epilogue warp counts a finished MLP1 item into tile_done[tile] behind a fence, and
+// the producer waits (bounded) for the tile's count before it requests the tile's rows.  MLP1 items wait for
+// nothing and every CTA is resident (one per SM), so the MLP2 waits always end.
 __global__ void __launch_bounds__(kThreads, 1)
-expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
-                   const GemmArgs p) {
+expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w1, const __grid_constant__ CUtensorMap tm_x1,
+                   const __grid_constant__ CUtensorMap tm_w2, const __grid_constant__ CUtensorMap tm_x2,
+                   const GemmArgs pa, const GemmArgs pb, const MlpFuse f) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t *smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -116,56 +130,95 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     tmem_relinquish();
   }
   if (warp == kProducerWarp && lane == 0) {
-    prefetch_tensormap(&tm_w);
-    prefetch_tensormap(&tm_x);
+    if (f.phase_begin == 0) { prefetch_tensormap(&tm_w1); prefetch_tensormap(&tm_x1); }
+    if (f.phase_end == 2) { prefetch_tensormap(&tm_w2); prefetch_tensormap(&tm_x2); }
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int n_work = *p.n_work;
-  const int K = p.K;
-  const int nkc = p.n_kchunks;
+  // Items of a phase are dealt round-robin.  In a fused launch the MLP2 deal starts where the MLP1 deal
+  // ended, so that the CTAs with one MLP1 item more are not also the ones with one MLP2 item more.
+  const int n_work1 = *pa.n_work;
+  auto first_item = [&](int phase) -> int {
+    if (phase == 0 || f.phase_begin != 0) return static_cast<int>(blockIdx.x);
+    const int g = static_cast<int>(gridDim.x);
+    return (static_cast<int>(blockIdx.x) + g - n_work1 % g) % g;
+  };
+  unsigned int *status = pa.status;
 
   if (warp == kProducerWarp) {
     // ------------------------------------------------------------- TMA producer
     // The warp stays converged; one elected lane issues the copies.
     uint32_t item = 0, s = 0, e_par = 1u;   // a fresh stage passes the first wait
     bool ok = true;
+    bool all_done = f.tile_done == nullptr;   // every MLP1 item of the launch is finished: no more checks
     const uint64_t w_policy = l2_policy_evict_first();
+   for (int phase = f.phase_begin; ok && phase < f.phase_end; ++phase) {
+    const bool second = phase != 0;
+    const CUtensorMap *tm_w = second ? &tm_w2 : &tm_w1, *tm_x = second ? &tm_x2 : &tm_x1;
+    const WorkItem *work = second ? pb.work : pa.work;
+    const int n_work = second ? *pb.n_work : n_work1;
+    const int nkc = second ? pb.n_kchunks : pa.n_kchunks, n_ntiles = second ? pb.n_ntiles : pa.n_ntiles;
+    const uint8_t *sfa = second ? pb.sfa : pa.sfa, *w_tiles = second ? pb.w_tiles : pa.w_tiles;
+    const int sfa_tile_stride = second ? pb.sfa_tile_stride : pa.sfa_tile_stride;
+    const int first = first_item(phase);
     WorkItem w_next = {};
-    if (static_cast<int>(blockIdx.x) < n_work) w_next = p.work[blockIdx.x];
-    for (int wi = blockIdx.x; ok && wi < n_work; wi += gridDim.x) {
+    if (first < n_work) w_next = work[first];
+    for (int wi = first; ok && wi < n_work; wi += gridDim.x) {
       const WorkItem w = w_next;
-      if (wi + static_cast<int>(gridDim.x) < n_work) w_next = p.work[wi + gridDim.x];
+      if (wi + static_cast<int>(gridDim.x) < n_work) w_next = work[wi + gridDim.x];
       for (int blk = 0; ok && blk < w.nblk; ++blk, ++item) {
+        if (second && !all_done) {
+          // the SwiGLU rows of this token tile: all MLP1 items of the tile (one per weight block; the index
+          // kernel emits single-block items) must have been counted in by their 16 epilogue warps
+          const long long t0 = clock64();
+          for (uint32_t spin = 0;; ++spin) {
+            const uint32_t total = __shfl_sync(0xffffffffu, ld_acquire_gpu(f.tile_done + f.total_slot), 0);
+            if (total >= static_cast<uint32_t>(kEpiWarps) * static_cast<uint32_t>(n_work1)) { all_done = true; break; }
+            const uint32_t mine = __shfl_sync(0xffffffffu, ld_acquire_gpu(f.tile_done + w.tile), 0);
+            if (mine >= static_cast<uint32_t>(f.done_per_tile)) break;
+            if ((spin & 15u) == 15u) {
+              const bool late = __any_sync(0xffffffffu, clock64() - t0 > kWaitCycles);
+              if (late || __any_sync(0xffffffffu, *abort_flag != 0u)) {
+                if (late && lane == 0) { *abort_flag = 1u; atomicOr(status, ST_WAIT_AREADY); }
+                ok = false;
+                break;
+              }
+            }
+          }
+          if (!ok) break;
+          // written with ordinary stores on other SMs, read by the copy engine here
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
         // activation scale atom of this token tile, through its own ring so that the producer never waits
         // for an epilogue; a slot is free once the MMAs of the item that used it are done
         const uint32_t q = item % kSfaSlots;
-        if (!mbar_wait_warp(sfa_empty_bar(q), ((item / kSfaSlots) & 1u) ^ 1u, abort_flag, p.status, ST_WAIT_EMPTY)) { ok = false; break; }
+        if (!mbar_wait_warp(sfa_empty_bar(q), ((item / kSfaSlots) & 1u) ^ 1u, abort_flag, status, ST_WAIT_EMPTY)) { ok = false; break; }
         if (elect_one()) {
           mbar_arrive_expect_tx(sfa_full_bar(q), kSfAtomBytes);
-          bulk_load(smem_base + kSfaOff + q * kSfAtomBytes, p.sfa + static_cast<size_t>(w.tile) * p.sfa_tile_stride,
+          bulk_load(smem_base + kSfaOff + q * kSfAtomBytes, sfa + static_cast<size_t>(w.tile) * sfa_tile_stride,
                     kSfAtomBytes, sfa_full_bar(q));
         }
-        const uint32_t tile0 = (static_cast<uint32_t>(w.expert) * p.n_ntiles + w.ntile + blk) * nkc;
+        const uint32_t tile0 = (static_cast<uint32_t>(w.expert) * n_ntiles + w.ntile + blk) * nkc;
         for (int kc = 0; kc < nkc; ++kc) {
-          if (!mbar_wait_warp(empty_bar(s), e_par, abort_flag, p.status, ST_WAIT_EMPTY)) { ok = false; break; }
+          if (!mbar_wait_warp(empty_bar(s), e_par, abort_flag, status, ST_WAIT_EMPTY)) { ok = false; break; }
           const uint32_t stage = smem_base + s * kStageBytes;
           if (elect_one()) {
             mbar_arrive_expect_tx(full_bar(s), kABytes + kWLoadBytes + kSfbChunkBytes);
             // the weight tile first: it has the longer way (HBM; the activations come from L2).  Weights pass
             // through once per step: they must not push the activations and the results out of L2
-            tma_load_3d_hint(stage + kABytes, &tm_w, 0, 0, static_cast<int>(tile0 + kc), full_bar(s), w_policy);
-            bulk_load_hint(stage + kABytes + kWBytes, p.w_tiles + static_cast<size_t>(tile0 + kc) * kWTileStride + kWTileCodes,
+            tma_load_3d_hint(stage + kABytes, tm_w, 0, 0, static_cast<int>(tile0 + kc), full_bar(s), w_policy);
+            bulk_load_hint(stage + kABytes + kWBytes, w_tiles + static_cast<size_t>(tile0 + kc) * kWTileStride + kWTileCodes,
                            kSfbChunkBytes, full_bar(s), w_policy);
-            tma_load_2d(stage, &tm_x, 0, (w.tile * nkc + kc) * kTileM, full_bar(s));   // one contiguous 16 KB tile
+            tma_load_2d(stage, tm_x, 0, (w.tile * nkc + kc) * kTileM, full_bar(s));   // one contiguous 16 KB tile
           }
           if (++s == kStages) { s = 0; e_par ^= 1u; }
         }
       }
     }
+   }
     if (!ok) {  // give copies in flight time to land before the CTA's shared memory is released
       for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     }
@@ -178,23 +231,29 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     uint32_t item = 0, s = 0, f_par = 0, sfb_sel = 0;
     bool ok = true;
     const uint64_t desc_fixed = smem_desc_sw128(0);
+   for (int phase = f.phase_begin; ok && phase < f.phase_end; ++phase) {
+    const bool second = phase != 0;
+    const WorkItem *work = second ? pb.work : pa.work;
+    const int n_work = second ? *pb.n_work : n_work1;
+    const int K = second ? pb.K : pa.K, nkc = second ? pb.n_kchunks : pa.n_kchunks;
     const int full_chunks = K / kChunkK, tail_steps = (K % kChunkK) / 32;
+    const int first = first_item(phase);
     uint32_t nblk_next = 0;
-    if (static_cast<int>(blockIdx.x) < n_work) nblk_next = p.work[blockIdx.x].nblk;
-    for (int wi = blockIdx.x; ok && wi < n_work; wi += gridDim.x) {
+    if (first < n_work) nblk_next = work[first].nblk;
+    for (int wi = first; ok && wi < n_work; wi += gridDim.x) {
       const uint32_t nblk = nblk_next;
-      if (wi + static_cast<int>(gridDim.x) < n_work) nblk_next = p.work[wi + gridDim.x].nblk;
+      if (wi + static_cast<int>(gridDim.x) < n_work) nblk_next = work[wi + gridDim.x].nblk;
       for (uint32_t blk = 0; ok && blk < nblk; ++blk, ++item) {
         const uint32_t d = item & 1u;
-        if (!mbar_wait_warp(dempty_bar(d), ((item >> 1) & 1u) ^ 1u, abort_flag, p.status, ST_WAIT_DEMPTY)) { ok = false; break; }
+        if (!mbar_wait_warp(dempty_bar(d), ((item >> 1) & 1u) ^ 1u, abort_flag, status, ST_WAIT_DEMPTY)) { ok = false; break; }
         const uint32_t q = item % kSfaSlots;
-        if (!mbar_wait_warp(sfa_full_bar(q), (item / kSfaSlots) & 1u, abort_flag, p.status, ST_WAIT_AREADY)) { ok = false; break; }
+        if (!mbar_wait_warp(sfa_full_bar(q), (item / kSfaSlots) & 1u, abort_flag, status, ST_WAIT_AREADY)) { ok = false; break; }
         tc_fence_after();
         const uint32_t sfa_t = tm + kSfaCol0 + 4 * d;
         if (elect_one()) tmem_cp_sf_atom(sfa_t, smem_base + kSfaOff + q * kSfAtomBytes);
         const uint32_t d_addr = tm + d * kAccBufCols;
         for (int kc = 0; kc < nkc; ++kc) {
-          if (!mbar_wait_warp(full_bar(s), f_par, abort_flag, p.status, ST_WAIT_FULL)) { ok = false; break; }
+          if (!mbar_wait_warp(full_bar(s), f_par, abort_flag, status, ST_WAIT_FULL)) { ok = false; break; }
           const uint32_t stage = smem_base + s * kStageBytes;
           const uint32_t sfb_t = tm + kSfbCol0 + 8 * sfb_sel;
           const uint64_t adesc = desc_fixed | (stage >> 4), bdesc = desc_fixed | ((stage + kABytes) >> 4);
@@ -222,6 +281,7 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         }
       }
     }
+   }
   } else {
     // ------------------------------------------------------------- epilogue warps
     // Warp w reads tensor-memory lanes 32*(w%4).., i.e. accumulator rows 32q + l: token 16q + l/2, high
@@ -231,25 +291,32 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     const uint32_t lane_field = static_cast<uint32_t>(quad * 32) << 16;
     const int odd = lane & 1;
     const int tok = quad * 16 + (lane >> 1);
-    const float h_scale = exp2f(static_cast<float>(-p.h_exp));
+    const float h_scale = exp2f(static_cast<float>(-pa.h_exp));
     uint32_t item = 0;
     bool ok = true;
+   for (int phase = f.phase_begin; ok && phase < f.phase_end; ++phase) {
+    const bool second = phase != 0;
+    const WorkItem *work = second ? pb.work : pa.work;
+    const int n_work = second ? *pb.n_work : n_work1;
+    const int R = second ? pb.R : pa.R;
+    const __nv_bfloat16 *bias = second ? pb.bias : pa.bias;
+    const int first = first_item(phase);
     WorkItem w_next = {};
-    if (static_cast<int>(blockIdx.x) < n_work) w_next = p.work[blockIdx.x];
-    for (int wi = blockIdx.x; ok && wi < n_work; wi += gridDim.x) {
+    if (first < n_work) w_next = work[first];
+    for (int wi = first; ok && wi < n_work; wi += gridDim.x) {
      const WorkItem w = w_next;
-     if (wi + static_cast<int>(gridDim.x) < n_work) w_next = p.work[wi + gridDim.x];  // in flight during the wait below
+     if (wi + static_cast<int>(gridDim.x) < n_work) w_next = work[wi + gridDim.x];  // in flight during the wait below
      for (int blk = 0; ok && blk < w.nblk; ++blk, ++item) {
       const uint32_t d = item & 1u;
-      if (!mbar_wait(dfull_bar(d), (item >> 1) & 1u, abort_flag, p.status, ST_WAIT_DFULL)) { ok = false; break; }
+      if (!mbar_wait(dfull_bar(d), (item >> 1) & 1u, abort_flag, status, ST_WAIT_DFULL)) { ok = false; break; }
       tc_fence_after();
       const int n0 = (w.ntile + blk) * kTileN;
       const bool tok_ok = tok < w.ntok;
-      const __nv_bfloat16 *bias_row = p.bias + static_cast<size_t>(w.expert) * p.R;
+      const __nv_bfloat16 *bias_row = bias + static_cast<size_t>(w.expert) * R;
       const uint32_t acc = tmem_base + lane_field + d * kAccBufCols;
       // chunks of this warp that hold rows of the matrix (rows past it are zero-filled and produce nothing)
       const int c_beg = half * kEpiChunks;
-      const int c_end = min(min(c_beg + kEpiChunks, kTileN / 16), (p.R - n0 + 15) / 16);
+      const int c_end = min(min(c_beg + kEpiChunks, kTileN / 16), (R - n0 + 15) / 16);
 
       auto process = [&](const uint32_t (&v)[16], int c0) {
         // Sum of the high and low partial products of a token (adjacent lanes).  Each lane of the pair keeps 8
@@ -264,10 +331,10 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
           const float give = odd ? fe : fo;
           tot[i] = mine + __shfl_xor_sync(0xffffffffu, give, 1);
         }
-        if (MODE == 1) {
+        if (!second) {
           const int nc = n0 + c0 + 8 * odd;  // first of this lane's 8 columns
           float b[8];
-          if (nc < p.R) {
+          if (nc < R) {
             const uint4 bv = __ldg(reinterpret_cast<const uint4 *>(bias_row + nc));
             const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
 #pragma unroll
@@ -282,24 +349,24 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
           float hs[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i)
-            hs[i] = swiglu_clamped(tot[2 * i] + b[2 * i], tot[2 * i + 1] + b[2 * i + 1], p.limit, p.alpha) * h_scale;
+            hs[i] = swiglu_clamped(tot[2 * i] + b[2 * i], tot[2 * i + 1] + b[2 * i + 1], pa.limit, pa.alpha) * h_scale;
           const uint32_t hi4 = pack_e4m3x4(hs[0], hs[1], hs[2], hs[3]);
           float r[4];
 #pragma unroll
           for (int i = 0; i < 4; ++i) r[i] = (hs[i] - e4m3_to_float((hi4 >> (8 * i)) & 0xffu)) * 16.0f;
           const uint32_t lo4 = pack_e4m3x4(r[0], r[1], r[2], r[3]);
-          const int j = p.hq_joff + (nc >> 1);  // this lane's 4 intermediate features, as columns of MLP2's k window
-          if (tok_ok && nc < p.R) {
+          const int j = pa.hq_joff + (nc >> 1);  // this lane's 4 intermediate features, as columns of MLP2's k window
+          if (tok_ok && nc < R) {
             // MLP2's activation tiles: [tile][k slice][128 rows][128 bytes]
-            uint8_t *dst = p.hq_out + ((static_cast<size_t>(w.tile) * p.hq_nkc + (j >> 7)) * kTileM + 2 * tok) * kChunkK + (j & 127);
+            uint8_t *dst = pa.hq_out + ((static_cast<size_t>(w.tile) * pa.hq_nkc + (j >> 7)) * kTileM + 2 * tok) * kChunkK + (j & 127);
             *reinterpret_cast<uint32_t *>(dst) = hi4;
             *reinterpret_cast<uint32_t *>(dst + kChunkK) = lo4;
           }
         } else {
           const int na = n0 + c0 + 8 * odd;  // first of this lane's 8 columns
-          if (tok_ok && na < p.R) {          // R is a multiple of 32 here, so the whole chunk is inside
+          if (tok_ok && na < R) {          // R is a multiple of 32 here, so the whole chunk is inside
             float b[8];
-            if (p.add_bias) {
+            if (pb.add_bias) {
               const uint4 bv = __ldg(reinterpret_cast<const uint4 *>(bias_row + na));
               const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
 #pragma unroll
@@ -322,8 +389,8 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
               const __half2 hh = __floats2half2_rn(y0, y1);
               o[i] = *reinterpret_cast<const uint32_t *>(&hh);
             }
-            if (big > 65504.f) atomicOr(p.status, ST_Y_RANGE);
-            __half *dst = p.y_out + static_cast<size_t>(w.row0 + tok) * p.ld_out + na;
+            if (big > 65504.f) atomicOr(status, ST_Y_RANGE);
+            __half *dst = pb.y_out + static_cast<size_t>(w.row0 + tok) * pb.ld_out + na;
             *reinterpret_cast<uint4 *>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
           }
         }
@@ -345,8 +412,18 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(dempty_bar(d));
+      if (!second && f.tile_done != nullptr) {
+        // this warp's SwiGLU rows of the item are written: fence by every lane, then one count per warp
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) {
+          atomicAdd(f.tile_done + w.tile, 1u);
+          atomicAdd(f.tile_done + f.total_slot, 1u);
+        }
+      }
      }
     }
+   }
   }
 
   tc_fence_before();
@@ -358,18 +435,16 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 }
 
 cudaError_t expert_gemm_init() {
-  cudaError_t e = cudaFuncSetAttribute(expert_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-  if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(expert_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+  return cudaFuncSetAttribute(expert_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
 }
 
-void launch_expert_gemm_mlp1(const CUtensorMap &tm_w, const CUtensorMap &tm_x, const GemmArgs &a, int grid,
-                             cudaStream_t s) {
-  expert_gemm_kernel<1><<<grid, kThreads, kSmemBytes, s>>>(tm_w, tm_x, a);
+// Phases [f.phase_begin, f.phase_end) of the expert MLP in one launch: both in the usual call, one at a
+// time (two launches, f.tile_done = nullptr) on request.
+void launch_expert_mlp(const CUtensorMap &tm_w1, const CUtensorMap &tm_x1, const GemmArgs &a, const CUtensorMap &tm_w2,
+                       const CUtensorMap &tm_x2, const GemmArgs &b, const MlpFuse &f, int grid, cudaStream_t s) {
+  expert_gemm_kernel<<<grid, kThreads, kSmemBytes, s>>>(tm_w1, tm_x1, tm_w2, tm_x2, a, b, f);
 }
-void launch_expert_gemm_mlp2(const CUtensorMap &tm_w, const CUtensorMap &tm_x, const GemmArgs &a, int grid,
-                             cudaStream_t s) {
-  expert_gemm_kernel<2><<<grid, kThreads, kSmemBytes, s>>>(tm_w, tm_x, a);
-}
+
+int expert_mlp_done_per_tile(int n_ntiles1) { return kEpiWarps * n_ntiles1; }
 
 }  // namespace moe

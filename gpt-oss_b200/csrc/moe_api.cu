@@ -222,7 +222,8 @@ int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_b
     c->launches += 4;
   }
   launch_build_index(c->topk_idx, c->counts, T, E, K, n_nt1, n_nt2, c->offsets, c->tile_base, c->pair_row,
-                     c->row_token, c->pair_slot, c->work1, c->work2, c->n_work, c->max_work1, c->max_work2, status, s);
+                     c->row_token, c->pair_slot, c->tile_done, c->max_tiles, c->work1, c->work2, c->n_work, c->max_work1,
+                     c->max_work2, status, s);
   if (tpcall) {   // now the gathered rows: this rank's push is complete (side stream), then every peer's
     CU_TRY(c, cudaStreamWaitEvent(s, c->ev_join, 0));
     launch_tp_signal_wait(c->peers, c->tp_flags, tp, rank, kTpPhaseGather, c->tp_epoch, status, s);
@@ -246,14 +247,26 @@ int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_b
     a.hq_out = c->hq; a.hq_joff = c->joff; a.hq_nkc = (c->Kw + kChunkK - 1) / kChunkK; a.y_out = nullptr; a.ld_out = c->Kw;
     a.h_exp = c->h_exp;
     a.limit = c->cfg.swiglu_limit; a.alpha = c->cfg.swiglu_alpha; a.status = status;
-    launch_expert_gemm_mlp1(w.tm_w1, c->tm_x1, a, c->sm_count, s);
-    mark();
     GemmArgs b = a;
     b.work = c->work2; b.n_work = c->n_work + 1; b.K = c->Kw; b.R = H;
     b.n_kchunks = (c->Kw + kChunkK - 1) / kChunkK; b.n_ntiles = n_nt2;
     b.w_tiles = w.w2_tiles; b.sfa = c->sfa_h; b.sfa_tile_stride = 0; b.bias = w.b2; b.add_bias = add_b2;
     b.hq_out = nullptr; b.y_out = c->ybuf; b.ld_out = H;
-    launch_expert_gemm_mlp2(w.tm_w2, c->tm_x2, b, c->sm_count, s);
+    MlpFuse fuse{};
+    fuse.total_slot = c->max_tiles;
+    fuse.done_per_tile = expert_mlp_done_per_tile(n_nt1);
+    if (flags & MOE_FWD_SPLIT_MLP) {   // MLP1 and MLP2 as two launches
+      fuse.phase_begin = 0; fuse.phase_end = 1; fuse.tile_done = nullptr;
+      launch_expert_mlp(w.tm_w1, c->tm_x1, a, w.tm_w2, c->tm_x2, b, fuse, c->sm_count, s);
+      mark();
+      fuse.phase_begin = 1; fuse.phase_end = 2;
+      launch_expert_mlp(w.tm_w1, c->tm_x1, a, w.tm_w2, c->tm_x2, b, fuse, c->sm_count, s);
+    } else {                           // one launch; the MLP2 stage of a profile is then empty
+      fuse.phase_begin = 0; fuse.phase_end = 2; fuse.tile_done = c->tile_done;
+      launch_expert_mlp(w.tm_w1, c->tm_x1, a, w.tm_w2, c->tm_x2, b, fuse, c->sm_count, s);
+      mark();
+      c->launches -= 1;
+    }
   }
   mark();
   if (!tpcall) {
@@ -389,6 +402,7 @@ int moe_create(const moe_config *cfg, moe_handle *out) {
   CU_TRY(c, cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming));
   const int n_nt1 = (c->R1 + kTileN - 1) / kTileN, n_nt2 = (c->H + kTileN - 1) / kTileN;
   c->max_tiles = c->max_pairs / kTokTile + c->E + 1;
+  if ((rc = dev_alloc(c, &c->tile_done, static_cast<size_t>(c->max_tiles) + 1))) return rc;
   c->max_work1 = c->max_tiles * n_nt1;
   c->max_work2 = c->max_tiles * n_nt2;
   // SwiGLU outputs are bounded by limit*(limit+1); they are stored as e4m3(h * 2^-h_exp) with the
@@ -452,7 +466,7 @@ int moe_destroy(moe_handle c) {
   for (cudaEvent_t e : c->prof_events) cudaEventDestroy(e);
   for (cudaEvent_t e : c->prof_pool) cudaEventDestroy(e);
   cudaFree(c->t_in); cudaFree(c->t_norm); cudaFree(c->logits); cudaFree(c->router_part); cudaFree(c->topk_idx); cudaFree(c->topk_w); cudaFree(c->counts);
-  cudaFree(c->offsets); cudaFree(c->pair_row); cudaFree(c->row_token); cudaFree(c->pair_slot); cudaFree(c->xperm); cudaFree(c->hbuf);
+  cudaFree(c->offsets); cudaFree(c->pair_row); cudaFree(c->row_token); cudaFree(c->pair_slot); cudaFree(c->tile_done); cudaFree(c->xperm); cudaFree(c->hbuf);
   cudaFree(c->ybuf); cudaFree(c->out_f32); cudaFree(c->out_bf16); cudaFree(c->work1); cudaFree(c->work2);
   cudaFree(c->n_work); cudaFree(c->status);
   cudaFree(c->xq); cudaFree(c->hq); cudaFree(c->sfa_x); cudaFree(c->sfa_h); cudaFree(c->tile_base);

@@ -104,6 +104,16 @@ struct GemmArgs {
   unsigned int *status;
 };
 
+// How one launch of the expert GEMM kernel runs: which phases (0 = MLP1, 1 = MLP2), and where the MLP1 items
+// of a token tile are counted so that the tile's MLP2 items, in the same launch, know when its SwiGLU rows
+// are complete.
+struct MlpFuse {
+  int phase_begin, phase_end;
+  unsigned int *tile_done;   // [total_slot + 1], zeroed by build_index_kernel; nullptr: phases in separate launches
+  int total_slot;            // the last word counts the MLP1 items of all tiles
+  int done_per_tile;         // epilogue warps x MLP1 weight blocks
+};
+
 struct LayerWeights {
   bool loaded = false;
   // MLP1 weights as the GEMM streams them: one 16 KB tile per (expert, 240-row block, 128-wide slice of k),
@@ -148,6 +158,7 @@ struct moe_ctx {
   int *pair_row = nullptr;          // local_ids_g         [max_rows, K]
   int *row_token = nullptr;         // expert_row_token_g  [max_pairs]
   int *pair_slot = nullptr;         // row of the high term of (token, k) in xq [max_rows, K]
+  unsigned int *tile_done = nullptr;   // [max_tiles + 1] MlpFuse::tile_done
   __half *xperm = nullptr;          // expert_input_buffer [max_pairs, H]   fp16 (validation GEMM only)
   __half *hbuf = nullptr;           // gate_up             [max_pairs, Dl]  fp16 (validation GEMM only)
   uint8_t *xq = nullptr;            // expert_input_buffer as e4m3 high/low rows, [max_tiles][k slices][128 rows][128 B]
@@ -233,7 +244,7 @@ void launch_topk_softmax(float *logits, const float *partial, int splits, const 
                          int row_offset = 0);
 void launch_count_experts(const int *idx, int n, int E, int *counts, cudaStream_t s);
 void launch_build_index(const int *topk_idx, const int *counts, int T, int E, int K, int n_ntiles1, int n_ntiles2,
-                        int *offsets, int *tile_base, int *pair_row, int *row_token, int *pair_slot, WorkItem *work1,
+                        int *offsets, int *tile_base, int *pair_row, int *row_token, int *pair_slot, unsigned int *tile_done, int tile_done_total_slot, WorkItem *work1,
                         WorkItem *work2, int *n_work, int max_work1, int max_work2, unsigned int *status,
                         cudaStream_t s);
 void launch_quantize_rows(const __nv_bfloat16 *t, const int *pair_slot, int T, int K, uint8_t *xq, uint8_t *sfa, int H,
@@ -250,10 +261,9 @@ void launch_rmsnorm_rows(const __nv_bfloat16 *x, const __nv_bfloat16 *w, __nv_bf
 
 // expert_gemm_sm100.cu
 cudaError_t expert_gemm_init();
-void launch_expert_gemm_mlp1(const CUtensorMap &tm_w, const CUtensorMap &tm_x, const GemmArgs &a, int grid,
-                             cudaStream_t s);
-void launch_expert_gemm_mlp2(const CUtensorMap &tm_w, const CUtensorMap &tm_x, const GemmArgs &a, int grid,
-                             cudaStream_t s);
+void launch_expert_mlp(const CUtensorMap &tm_w1, const CUtensorMap &tm_x1, const GemmArgs &a, const CUtensorMap &tm_w2,
+                       const CUtensorMap &tm_x2, const GemmArgs &b, const MlpFuse &f, int grid, cudaStream_t s);
+int expert_mlp_done_per_tile(int n_ntiles1);
 
 // tp_collectives.cu
 // Both pushes send rows [row0, row0 + n_rows) of this rank's rows_local rows (n_rows < 0: all of them).

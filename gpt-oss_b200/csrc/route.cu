@@ -105,7 +105,7 @@ __global__ void __launch_bounds__(1024)
 build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ counts, int T, int E, int K,
                    int n_ntiles1, int n_ntiles2, int *__restrict__ offsets, int *__restrict__ tile_base,
                    int *__restrict__ pair_row, int *__restrict__ row_token, int *__restrict__ pair_slot,
-                   WorkItem *__restrict__ work1,
+                   unsigned int *__restrict__ tile_done, int tile_done_total_slot, WorkItem *__restrict__ work1,
                    WorkItem *__restrict__ work2, int *__restrict__ n_work, int max_work1, int max_work2,
                    unsigned int *status) {
   __shared__ int s_red[2][32];
@@ -136,6 +136,9 @@ build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ cou
     tile_base[e] = tiles_before;
     if (e == E - 1) { offsets[E] = off + cnt; tile_base[E] = tiles_before + ntt; }
   }
+  // completion counters of the fused expert MLP launch: this expert's token tiles, and the total
+  for (int i = tid; i < ntt; i += blockDim.x) tile_done[tiles_before + i] = 0u;
+  if (e == E - 1 && tid == 0) tile_done[tile_done_total_slot] = 0u;
 
   // Stable compaction in ascending token order.  Warp w owns the contiguous token range [w*per, (w+1)*per):
   // a first walk counts the range's hits with ballots, one block-wide barrier turns the warps' counts into
@@ -219,10 +222,11 @@ build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ cou
 
 void launch_build_index(const int *topk_idx, const int *counts, int T, int E, int K, int n_ntiles1, int n_ntiles2,
                         int *offsets, int *tile_base, int *pair_row, int *row_token, int *pair_slot,
-                        WorkItem *work1, WorkItem *work2, int *n_work, int max_work1, int max_work2,
+                        unsigned int *tile_done, int tile_done_total_slot, WorkItem *work1, WorkItem *work2, int *n_work, int max_work1, int max_work2,
                         unsigned int *status, cudaStream_t s) {
   build_index_kernel<<<E, T > 2048 ? 1024 : 256, 0, s>>>(topk_idx, counts, T, E, K, n_ntiles1, n_ntiles2, offsets, tile_base,
-                                       pair_row, row_token, pair_slot, work1, work2, n_work, max_work1, max_work2, status);
+                                       pair_row, row_token, pair_slot, tile_done, tile_done_total_slot, work1, work2, n_work,
+                                                          max_work1, max_work2, status);
 }
 
 // ---------------------------------------------------------------------------

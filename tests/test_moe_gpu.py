@@ -102,7 +102,7 @@ def run_block(pkg, layer, tokens, flags=0, max_rows=None, keep_f32=True):
     return blk, out
 
 
-@pytest.mark.parametrize("flags", [0, 1, 4], ids=["tcgen05", "simt", "split_router"])
+@pytest.mark.parametrize("flags", [0, 1, 4, 8], ids=["tcgen05", "simt", "split_router", "split_mlp"])
 @pytest.mark.parametrize("name", golden_cases())
 def test_golden_fixture(name, flags, pkg, synth):
     layer, tokens, z = _load_case(name, synth)
@@ -181,7 +181,7 @@ def test_shapes_against_oracle(E, H, D, T, zipf, pkg, synth, port):
     layer = synth.make_layer(E, H, D, seed=E + T, zipf_s=zipf)
     tokens = synth.make_tokens(T, H, seed=H + T)
     ref_logits, ref_i, ref_w, ref_out = port.moe_layer(layer, tokens)
-    for flags in (0, 1, 4):
+    for flags in (0, 1, 4, 8):
         blk, out = run_block(pkg, layer, tokens, flags=flags)
         try:
             same = check_selection(blk.debug(pkg.DBG_TOPK_IDX), ref_i, ref_logits)
@@ -263,6 +263,28 @@ def test_headline_shape_sampled_rows_against_oracle(zipf, layer_120b, pkg, synth
         assert counts.sum() == 4 * T
         if zipf is not None:
             assert counts.max() > T // 2 and (counts == 0).any()   # the skew the case is about
+    finally:
+        blk.close()
+
+
+@pytest.mark.parametrize("zipf", [None, 1.2], ids=["uniform", "zipf1.2"])
+def test_one_launch_and_two_launch_mlp_agree_bitwise(zipf, layer_120b, pkg, synth):
+    """MLP1 and MLP2 in one launch (an MLP2 item waits, inside the kernel, for the MLP1 items of its token tile)
+    against the same kernel launched once per phase: the arithmetic is the same, so every output bit must be;
+    a tile read before it was complete would show here.  Full benchmark size, several passes."""
+    E, H, D, T = 128, 2880, 2880, 1856
+    layer = dict(layer_120b)
+    if zipf is not None:
+        layer["router_b"] = synth.zipf_router_bias(E, zipf)
+    blk = pkg.MoeBlock(H, D, E, max_rows=T)
+    try:
+        blk.load_layer(0, layer)
+        for seed in range(3):
+            tokens = synth.make_tokens(T, H, seed=40 + seed)
+            two = blk.forward_host(0, tokens, flags=pkg.FWD_SPLIT_MLP).copy()
+            for _ in range(3):
+                one = blk.forward_host(0, tokens)
+                assert np.array_equal(one, two)
     finally:
         blk.close()
 
