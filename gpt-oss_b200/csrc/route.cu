@@ -113,36 +113,9 @@ build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ cou
   const int e = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_warps = blockDim.x >> 5;   // 8, or 32 for batches whose selections 8 warps cannot hold in registers
 
-  // exclusive prefix over experts below e: rows and token tiles
-  int my_rows = 0, my_tiles = 0;
-  for (int i = tid; i < e; i += blockDim.x) {
-    const int c = counts[i];
-    my_rows += c;
-    my_tiles += (c + kTokTile - 1) / kTokTile;
-  }
-#pragma unroll
-  for (int off = 16; off; off >>= 1) {
-    my_rows += __shfl_xor_sync(0xffffffffu, my_rows, off);
-    my_tiles += __shfl_xor_sync(0xffffffffu, my_tiles, off);
-  }
-  if (lane == 0) { s_red[0][warp] = my_rows; s_red[1][warp] = my_tiles; }
-  __syncthreads();
-  int off = 0, tiles_before = 0;
-  for (int i = 0; i < n_warps; ++i) { off += s_red[0][i]; tiles_before += s_red[1][i]; }
-  const int cnt = counts[e];
-  const int ntt = (cnt + kTokTile - 1) / kTokTile;  // token tiles of this expert (rows e's tiles, in order)
-  if (tid == 0) {
-    offsets[e] = off;
-    tile_base[e] = tiles_before;
-    if (e == E - 1) { offsets[E] = off + cnt; tile_base[E] = tiles_before + ntt; }
-  }
-  // completion counters of the fused expert MLP launch: this expert's token tiles, and the total
-  for (int i = tid; i < ntt; i += blockDim.x) tile_done[tiles_before + i] = 0u;
-  if (e == E - 1 && tid == 0) tile_done[tile_done_total_slot] = 0u;
-
   // Stable compaction in ascending token order.  Warp w owns the contiguous token range [w*per, (w+1)*per):
-  // a first walk counts the range's hits with ballots, one block-wide barrier turns the warps' counts into
-  // starting positions, a second walk writes the rows.  No barrier per step.
+  // a first walk counts the range's hits with ballots, the block's one barrier turns the warps' counts into
+  // starting positions, a second walk writes the rows.
   const int per = ((T + n_warps - 1) / n_warps + 31) / 32 * 32;       // tokens per warp, whole ballot steps
   const int t_begin = warp * per, t_end = min(T, t_begin + per);
   auto hit_of = [&](int t) -> int {
@@ -160,13 +133,40 @@ build_index_kernel(const int *__restrict__ topk_idx, const int *__restrict__ cou
   int cached[kCached];
 #pragma unroll
   for (int j = 0; j < kCached; ++j) cached[j] = hit_of(t_begin + 32 * j + lane);
+
+  // exclusive prefix over experts below e: rows and token tiles (its loads travel with the ones above)
+  int my_rows = 0, my_tiles = 0;
+  for (int i = tid; i < e; i += blockDim.x) {
+    const int c = counts[i];
+    my_rows += c;
+    my_tiles += (c + kTokTile - 1) / kTokTile;
+  }
+#pragma unroll
+  for (int off = 16; off; off >>= 1) {
+    my_rows += __shfl_xor_sync(0xffffffffu, my_rows, off);
+    my_tiles += __shfl_xor_sync(0xffffffffu, my_tiles, off);
+  }
+  // first walk: this warp's hits
   const int t_rest = t_begin + 32 * kCached;
   int mine = 0;
 #pragma unroll
   for (int j = 0; j < kCached; ++j) mine += __popc(__ballot_sync(0xffffffffu, cached[j] >= 0));
   for (int t0 = t_rest; t0 < t_end; t0 += 32) mine += __popc(__ballot_sync(0xffffffffu, hit_of(t0 + lane) >= 0));
-  if (lane == 0) s_warp[warp] = mine;
-  __syncthreads();
+  if (lane == 0) { s_red[0][warp] = my_rows; s_red[1][warp] = my_tiles; s_warp[warp] = mine; }
+  __syncthreads();   // the only block-wide barrier: prefix partials and hit counts of all warps
+  int off = 0, tiles_before = 0;
+  for (int i = 0; i < n_warps; ++i) { off += s_red[0][i]; tiles_before += s_red[1][i]; }
+  const int cnt = counts[e];
+  const int ntt = (cnt + kTokTile - 1) / kTokTile;  // token tiles of this expert (rows e's tiles, in order)
+  if (tid == 0) {
+    offsets[e] = off;
+    tile_base[e] = tiles_before;
+    if (e == E - 1) { offsets[E] = off + cnt; tile_base[E] = tiles_before + ntt; }
+  }
+  // completion counters of the fused expert MLP launch: this expert's token tiles, and the total
+  for (int i = tid; i < ntt; i += blockDim.x) tile_done[tiles_before + i] = 0u;
+  if (e == E - 1 && tid == 0) tile_done[tile_done_total_slot] = 0u;
+
   int before = 0, total_hits = 0;
   for (int i = 0; i < n_warps; ++i) {
     before += i < warp ? s_warp[i] : 0;
