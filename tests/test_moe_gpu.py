@@ -191,7 +191,7 @@ def test_shapes_against_oracle(E, H, D, T, zipf, pkg, synth, port):
 
 
 @pytest.mark.parametrize("E,T", [(128, 1), (128, 130), (128, 1000), (128, 3000), (128, 10000), (32, 700), (24, 257),
-                                 (256, 300)])
+                                 (6, 100), (256, 300)])
 def test_router_forms_against_oracle(E, T, pkg, synth, port):
     """Router logits, selection, weights and histogram of the fused cluster kernel (1 to 8 k slices per token
     tile, by row count) and of the two-launch form (always taken above 128 experts), each against the oracle."""
@@ -210,6 +210,28 @@ def test_router_forms_against_oracle(E, T, pkg, synth, port):
             assert np.array_equal(blk.debug(pkg.DBG_COUNTS), np.bincount(idx.ravel(), minlength=E))
         finally:
             blk.close()
+
+
+@pytest.mark.parametrize("E,H,D,T,K", [
+    (8, 128, 64, 150, 2),     # two experts per token: the kernels' forms for any K
+    (16, 192, 96, 90, 6),
+    (8, 4096, 256, 70, 4),    # the widest row the quantiser takes (its 8-vector form)
+    (8, 3200, 256, 33, 4),
+])
+def test_other_top_k_and_wide_rows(E, H, D, T, K, pkg, synth, port):
+    layer = synth.make_layer(E, H, D, seed=E + T + K)
+    tokens = synth.make_tokens(T, H, seed=H + K)
+    ref_logits, ref_i, ref_w, ref_out = port.moe_layer(layer, tokens, top_k=K)
+    blk = pkg.MoeBlock(H, D, E, top_k=K, max_rows=T, keep_f32=True)
+    try:
+        blk.load_layer(0, layer)
+        out = blk.forward_host(0, tokens)
+        same = check_selection(blk.debug(pkg.DBG_TOPK_IDX), ref_i, ref_logits)
+        np.testing.assert_allclose(blk.debug(pkg.DBG_TOPK_W)[same], ref_w[same], rtol=2e-5, atol=1e-7)
+        check_output(out, blk.debug(pkg.DBG_OUT_F32), ref_out, synth, rows=same, label=f"E={E} H={H} K={K}")
+        assert np.array_equal(blk.debug(pkg.DBG_COUNTS), np.bincount(blk.debug(pkg.DBG_TOPK_IDX).ravel(), minlength=E))
+    finally:
+        blk.close()
 
 
 def test_shape20b_64_tokens(pkg, synth, port):
