@@ -614,7 +614,7 @@ def main():
     P = Tu * K
     R1 = 2 * Dl                      # this rank's MLP1 rows per expert
     # the expert MLP kernel (MLP1 + SwiGLU + MLP2 in one launch; its time is the profile's "mlp1" stage, the
-    # "mlp2" stage is then the gap between two events): weights, scales and biases of both matrices once, the
+    # "mlp2" stage is then empty): weights, scales and biases of both matrices once, the
     # two e4m3 terms of every gathered row in, the fp16 expert outputs out.  The SwiGLU rows in between are
     # written and read back inside the launch and are not counted.
     mlp_bytes = (active * (R1 * H // 2 + R1 * H // 32 + R1 * 2) + active * (H * Dl // 2 + H * Dl // 32 + H * 2)
@@ -653,7 +653,7 @@ def main():
                            "hbm_bound_ms": nbytes / hbm_peak / 1e6, "tensor_bound_ms": flops / tc_peak / 1e9,
                            "frac_of_min_time": max(nbytes / hbm_peak / 1e6, flops / tc_peak / 1e9) / ms_step},
         "stage_ms": {k: v / max(ncalls, 1) for k, v in stage_ms.items()},
-        "stage_ms_note": "'mlp1' is the one launch of the expert MLP kernel (MLP1 + SwiGLU + MLP2); 'mlp2' is empty",
+        "stage_ms_note": "'router' is the one launch that routes (router GEMM, top-k, softmax, histogram) and 'mlp1' the one launch of the expert MLP kernel (MLP1 + SwiGLU + MLP2); 'topk' and 'mlp2' launch nothing and are 0",
         "parity": parity,
         "checksum": loss_like,
     }

@@ -157,6 +157,11 @@ int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_b
     cudaEventRecord(ev, s);
     c->prof_events.push_back(ev);
   };
+  // a stage that launches nothing (its work went into the previous launch) shares that launch's event:
+  // recording another one would book the few microseconds an event costs as the stage's time
+  auto mark_empty = [&]() {
+    if (c->profiling) c->prof_events.push_back(nullptr);
+  };
   mark();
   if (norm_gain != nullptr && !tpcall) {   // step 0 of moe_gpu on one GPU: t = rmsnorm(x) * gain
     launch_rmsnorm_rows(residual, norm_gain, c->t_norm, rows, H, s);
@@ -166,6 +171,7 @@ int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_b
   // Routing of `n` rows at `src`: one fused launch (router GEMM, bias, top-k, softmax, histogram) when the
   // experts fit one CTA, else partial sums and topk_softmax_kernel.  In a TP call the selection goes to the
   // top-k buffers of every rank at this rank's row offset and the histogram is taken after the exchange.
+  bool routed_in_one_launch = false;
   auto route_rows = [&](const __nv_bfloat16 *src, int n) -> int {
     const int slices = (flags & MOE_FWD_SPLIT_ROUTER) ? 0 : router_fused_slices(n, H, E, c->sm_count, c->router_cluster);
     RouteOut ro = {};
@@ -175,6 +181,7 @@ int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_b
     bool ok;
     if (slices > 0) {
       ok = launch_router_fused(src, w.tm_router, n, H, E, slices, ro, status, s);
+      routed_in_one_launch = true;
       mark();
       c->launches -= 1;   // one launch where the tally below counts two
     } else {
@@ -189,7 +196,7 @@ int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_b
   };
   if (!tpcall) {
     if (int rc = route_rows(t, T)) return rc;
-    mark();
+    if (routed_in_one_launch) mark_empty(); else mark();
   } else {
     // The all-gather push runs on the side stream in two parts.  The first starts at once, beside the
     // routing of the same rows; the router's few peer stores (the selections, written to every rank) queue
@@ -233,6 +240,7 @@ int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_b
   else launch_quantize_rows(t, c->pair_slot, T, K, c->xq, c->sfa_x, H, s);
   mark();
   const int add_b2 = c->cfg.tp_rank == 0 ? 1 : 0;
+  bool mlp_in_one_launch = false;
   if (flags & MOE_FWD_SIMT_GEMM) {
     launch_simt_mlp1(w.w1_tiles, w.w1_scales_raw, w.b1, c->xperm, c->offsets, E, H, c->R1,
                      c->hbuf + c->joff, c->Kw, c->cfg.swiglu_limit, c->cfg.swiglu_alpha, P, s);
@@ -266,9 +274,10 @@ int forward_impl(moe_ctx *c, int layer, const __nv_bfloat16 *t, int rows, __nv_b
       launch_expert_mlp(w.tm_w1, c->tm_x1, a, w.tm_w2, c->tm_x2, b, fuse, c->sm_count, s);
       mark();
       c->launches -= 1;
+      mlp_in_one_launch = true;
     }
   }
-  mark();
+  if (mlp_in_one_launch) mark_empty(); else mark();
   if (!tpcall) {
     const bool partial = (flags & MOE_FWD_PARTIAL_F32) != 0;
     const bool keep_f32 = partial || (c->cfg.flags & MOE_CFG_KEEP_F32_OUT);
@@ -463,7 +472,7 @@ int moe_destroy(moe_handle c) {
   if (c->ev_join) cudaEventDestroy(c->ev_join);
   cudaFree(c->tp_partial); cudaFree(c->tp_flags);
   for (auto &w : c->layers) free_layer(w);
-  for (cudaEvent_t e : c->prof_events) cudaEventDestroy(e);
+  for (cudaEvent_t e : c->prof_events) if (e) cudaEventDestroy(e);
   for (cudaEvent_t e : c->prof_pool) cudaEventDestroy(e);
   cudaFree(c->t_in); cudaFree(c->t_norm); cudaFree(c->logits); cudaFree(c->router_part); cudaFree(c->topk_idx); cudaFree(c->topk_w); cudaFree(c->counts);
   cudaFree(c->offsets); cudaFree(c->pair_row); cudaFree(c->row_token); cudaFree(c->pair_slot); cudaFree(c->tile_done); cudaFree(c->xperm); cudaFree(c->hbuf);
@@ -695,14 +704,19 @@ int moe_profile_collect(moe_handle c, float *ms, int *n_calls) {
   const size_t calls = c->prof_events.size() / per;
   for (int i = 0; i < MOE_N_STAGES; ++i) ms[i] = 0.f;
   for (size_t k = 0; k < calls; ++k) {
-    CU_TRY(c, cudaEventSynchronize(c->prof_events[k * per + MOE_N_STAGES]));
+    CU_TRY(c, cudaEventSynchronize(c->prof_events[k * per + MOE_N_STAGES]));   // the last one is always recorded
+    cudaEvent_t from = c->prof_events[k * per];
     for (int i = 0; i < MOE_N_STAGES; ++i) {
+      cudaEvent_t to = c->prof_events[k * per + i + 1];
+      if (to == nullptr) continue;   // an empty stage: 0 ms, the next stage starts where this one did
       float t = 0.f;
-      CU_TRY(c, cudaEventElapsedTime(&t, c->prof_events[k * per + i], c->prof_events[k * per + i + 1]));
+      CU_TRY(c, cudaEventElapsedTime(&t, from, to));
       ms[i] += t;
+      from = to;
     }
   }
-  for (cudaEvent_t e : c->prof_events) c->prof_pool.push_back(e);
+  for (cudaEvent_t e : c->prof_events)
+    if (e != nullptr) c->prof_pool.push_back(e);
   c->prof_events.clear();
   *n_calls = static_cast<int>(calls);
   return MOE_OK;
