@@ -85,9 +85,9 @@ int moe_shard_range(int intermediate_dim, int tp_size, int tp_rank, int *start, 
 /* moe_forward.flags */
 #define MOE_FWD_SIMT_GEMM 1u    /* run the plain CUDA-core validation GEMM (fp16 operands) instead of tcgen05 */
 #define MOE_FWD_PARTIAL_F32 2u  /* TP: leave this rank's fp32 partial in the handle, write no output */
-#define MOE_FWD_SPLIT_MLP 8u    /* MLP1 and MLP2 as two launches of the expert GEMM kernel instead of one */
 #define MOE_FWD_SPLIT_ROUTER 4u /* route with the two-launch form (split-k partial sums, then top-k) that layers of more
                                    than 128 experts always take, instead of the fused cluster kernel */
+#define MOE_FWD_SPLIT_MLP 8u    /* MLP1 and MLP2 as two launches of the expert GEMM kernel instead of one */
 
 /* Replaces moe_gpu()/moe_gpu_120b() steps 2-8 (getp_run.cpp:2540, :2896): router,
  * top-k + softmax, permutation, MLP1 + SwiGLU, MLP2, weighted combine, for `rows`
